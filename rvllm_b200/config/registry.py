@@ -1,8 +1,8 @@
 """The one registry from an architecture's name to its configuration class.
 
 `architectures[0]` of config.json selects the entry, as in the reference
-(v3/crates/rvllm-core/src/config/model.rs:20-29,70-79); an unknown name is an error that
-lists the known ones.  A registered class needs `from_dict(obj, where)` and `to_spec()`.
+(v3/crates/rvllm-core/src/config/model.rs:20-29,70-79) - or, in files that carry it, the
+string `architecture`; an unknown name is an error that lists the known ones.  A registered class needs `from_dict(obj, where)` and `to_spec()`.
 """
 from __future__ import annotations
 
@@ -10,6 +10,7 @@ from typing import Any, Dict, Type
 
 from ..errors import ConfigError
 from .model_config import LlamaConfig, Qwen2Config, read_config_json
+from .tufirax_config import TufiraxConfig
 
 _ARCHITECTURES: Dict[str, Type] = {}
 
@@ -33,8 +34,10 @@ def known_architectures():
 
 def config_from_dict(obj: Dict[str, Any], where: str = "config.json"):
     archs = obj.get("architectures")
+    if archs is None and isinstance(obj.get("architecture"), str):
+        archs = [obj["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("missing key `architectures` (a list whose first entry names the model)", where)
+        raise ConfigError("missing key `architectures` (a list whose first entry names the model) or `architecture` (its name)", where)
     cls = _ARCHITECTURES.get(archs[0])
     if cls is None:
         raise ConfigError(f"unsupported architecture {archs[0]!r}; known: {', '.join(known_architectures())}", where)
@@ -49,3 +52,4 @@ def load_config(model_dir: str):
 
 register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("Qwen2ForCausalLM", Qwen2Config)
+register_architecture("Tufirax", TufiraxConfig)

@@ -91,10 +91,15 @@ class ModelSpec:
     embedding_hooks: Tuple[PartSpec, ...] = ()
     logit_hooks: Tuple[PartSpec, ...] = ()
     ignored_tensors: Tuple[str, ...] = ()  # fnmatch patterns of checkpoint tensors to skip
+    # "float32": the residual stream between the layers stays in 32 bits whatever the engine's type (the
+    # blocks then round a copy for their products); None: the stream has the activations' type
     eos_token_ids: Tuple[int, ...] = ()
+    residual_dtype: Optional[str] = None
 
     def validate(self) -> List[str]:
         problems = []
+        if self.residual_dtype not in (None, "float32"):
+            problems.append(f"residual_dtype {self.residual_dtype!r} is not known (None, float32)")
         for i, layer in enumerate(self.layers):
             for role, part in layer.parts.items():
                 if part.family not in ("mixer", "feed_forward", "norm"):

@@ -8,6 +8,11 @@
 // window of W keys it sees (p - W, p].  kv_head = head * nkv / nh.  A decoded token is the
 // case q_len = 1.  ctx_len <= 0 marks a padded row: zeros are written, no table is read.
 //
+// Options for mixers that want them: `softcap` > 0 replaces a scaled score s by
+// softcap * tanh(s / softcap); `sinks` (one float per query head) adds exp(sink_h) to the softmax
+// denominator - a key without a value, neither scaled nor capped; `gate` (float [tokens, heads])
+// multiplies each head's output.
+//
 // Cache layer layout: [num_pages, 2 (k, v), nkv, page_size, hd].
 #include "common.cuh"
 
@@ -18,7 +23,8 @@ __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __r
                                            const int* __restrict__ block_tables, const int* __restrict__ cu_seqlens,
                                            const int* __restrict__ ctx_lens, const int* __restrict__ token_seq,
                                            T* __restrict__ out, int n_tokens, int nh, int nkv, int hd,
-                                           int page_size, int max_blocks, float scale, int window) {
+                                           int page_size, int max_blocks, float scale, int window,
+                                           float softcap, const float* __restrict__ sinks, const float* __restrict__ gate) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -62,6 +68,7 @@ __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __r
             if (d < hd) s = fmaf(qv[i], rv_to_float(kp[d]), s);
         }
         s = rv_warp_sum(s);
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);     // exp(-inf) = 0 at the first key
         const float p = expf(s - m_new);
@@ -73,7 +80,16 @@ __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __r
         }
         m = m_new;
     }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    if (sinks) {
+        const float sk = sinks[h];
+        const float m_new = fmaxf(m, sk);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < MAX_DIMS_PER_LANE; ++i) acc[i] *= corr;
+    }
+    float inv = l > 0.f ? 1.0f / l : 0.f;
+    if (gate) inv *= gate[(size_t)t * nh + h];
 #pragma unroll
     for (int i = 0; i < MAX_DIMS_PER_LANE; ++i) {
         const int d = lane + 32 * i;
@@ -84,7 +100,8 @@ __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __r
 RV_EXPORT int rv_paged_attention_ref(const void* q, const void* cache, const int* block_tables,
                                      const int* cu_seqlens, const int* ctx_lens, const int* token_seq,
                                      void* out, int n_tokens, int nh, int nkv, int hd, int page_size,
-                                     int max_blocks, float scale, int window, int dtype, cudaStream_t stream) {
+                                     int max_blocks, float scale, int window, float softcap, const float* sinks,
+                                     const float* gate, int dtype, cudaStream_t stream) {
     if (n_tokens < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0) return RV_ERR_BAD_SIZE;
     if (hd > 32 * MAX_DIMS_PER_LANE) return RV_ERR_UNSUPPORTED;
     if (n_tokens == 0) return RV_OK;
@@ -93,11 +110,11 @@ RV_EXPORT int rv_paged_attention_ref(const void* q, const void* cache, const int
     if (dtype == RV_DTYPE_F32)
         RV_LAUNCH_ST = rv_launch(paged_attention_ref_kernel<float>, dim3(grid), dim3(warps * 32), 0, stream, 
             (const float*)q, (const float*)cache, block_tables, cu_seqlens, ctx_lens, token_seq, (float*)out,
-            n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window);
+            n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window, softcap, sinks, gate);
     else if (dtype == RV_DTYPE_BF16)
         RV_LAUNCH_ST = rv_launch(paged_attention_ref_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, cu_seqlens, ctx_lens, token_seq,
-            (__nv_bfloat16*)out, n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window);
+            (__nv_bfloat16*)out, n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window, softcap, sinks, gate);
     else
         return RV_ERR_BAD_DTYPE;
     return rv_launch_status();

@@ -1,0 +1,216 @@
+// Row-wise kernels for layers that normalise the OUTPUT of a sublayer into a float32 residual
+// stream, and for attention whose queries and keys are normalised over the whole projection:
+//
+//   residual_rmsnorm      r <- r + y / sqrt(mean(y^2) + eps) * gamma   (r float32; also a copy of the new r
+//                         in the activations' type, which the next sublayer's products read)
+//   act_mul               rows [gate | up] -> act(gate) * up, act = SiLU or the tanh form of GELU
+//   qk_norm_rope_write    rows [q | k | gate logits]: q and k each divided by the root mean square of their
+//                         WHOLE row part and multiplied by a weight of that width, the leading `rot` elements
+//                         of every head rotated (pairs i, i + rot/2), q written out, k written into the
+//                         token's cache slot as the key and - unnormalised, unrotated - as the value;
+//                         sigmoid of the gate logits written as float
+//   gated_group_rmsnorm   (y * silu(z)) normalised in equal parts of a row, times a weight
+//
+// All arithmetic is float; storage is float or bfloat16 per argument.  Any width.
+#include "common.cuh"
+
+__device__ __forceinline__ float rv_load_any(const void* p, int dtype, size_t i) {
+    return dtype == RV_DTYPE_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+__device__ __forceinline__ void rv_store_any(void* p, int dtype, size_t i, float v) {
+    if (dtype == RV_DTYPE_F32) ((float*)p)[i] = v;
+    else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
+}
+
+// ------------------------------------------------------------------ residual + RMSNorm of a sublayer's output
+__global__ void __launch_bounds__(256)
+residual_rmsnorm_kernel(const void* __restrict__ y, int y_dtype, const void* __restrict__ gamma, int gamma_dtype,
+                        const float* res_in, float* res_out, void* __restrict__ rounded, int rounded_dtype,
+                        int cols, float eps) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * cols;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float v = rv_load_any(y, y_dtype, base + i);
+        ss = fmaf(v, v, ss);
+    }
+    ss = rv_block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)cols + eps);
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        float v = rv_load_any(y, y_dtype, base + i) * r * rv_load_param(gamma, gamma_dtype, i);
+        if (res_in) v += res_in[base + i];
+        if (res_out) res_out[base + i] = v;
+        if (rounded) rv_store_any(rounded, rounded_dtype, base + i, v);
+    }
+}
+
+RV_EXPORT int rv_residual_rmsnorm(const void* y, int y_dtype, const void* gamma, int gamma_dtype, const float* res_in,
+                                  float* res_out, void* rounded, int rounded_dtype, int rows, int cols, float eps,
+                                  cudaStream_t stream) {
+    if (rows < 0 || cols <= 0) return RV_ERR_BAD_SIZE;
+    if ((y_dtype | gamma_dtype | rounded_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (rows == 0) return RV_OK;
+    RV_LAUNCH_ST = rv_launch(residual_rmsnorm_kernel, dim3(rows), dim3(cols >= 1024 ? 256 : 128), 0, stream, y, y_dtype, gamma,
+                             gamma_dtype, res_in, res_out, rounded, rounded_dtype, cols, eps);
+    return rv_launch_status();
+}
+
+// ------------------------------------------------------------------ activation-gated product
+__device__ __forceinline__ float rv_gelu_tanh(float z) {
+    const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    return 0.5f * z * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float rv_silu(float z) { return z / (1.0f + expf(-z)); }
+
+__global__ void act_mul_kernel(const void* __restrict__ gate_up, int in_dtype, void* __restrict__ out, int out_dtype,
+                               int inter, size_t total, int act) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / inter, c = i - row * inter;
+        const float g = rv_load_any(gate_up, in_dtype, row * 2 * inter + c);
+        const float u = rv_load_any(gate_up, in_dtype, row * 2 * inter + inter + c);
+        rv_store_any(out, out_dtype, i, (act == 1 ? rv_gelu_tanh(g) : rv_silu(g)) * u);
+    }
+}
+
+RV_EXPORT int rv_act_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int rows, int inter, int act,
+                         cudaStream_t stream) {
+    if (rows < 0 || inter <= 0) return RV_ERR_BAD_SIZE;
+    if ((in_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (act != 0 && act != 1) return RV_ERR_UNSUPPORTED;
+    if (rows == 0) return RV_OK;
+    const size_t total = (size_t)rows * inter;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    RV_LAUNCH_ST = rv_launch(act_mul_kernel, dim3(blocks), dim3(256), 0, stream, gate_up, in_dtype, out, out_dtype, inter, total, act);
+    return rv_launch_status();
+}
+
+// ------------------------------------------------------------------ whole-row q/k norm, rotation, cache write, gate
+// One block per token.  Row layout: [q: nh*hd | k: nkv*hd | gate logits: nh] (gate part only if gate_out).
+__global__ void __launch_bounds__(256)
+qk_norm_rope_write_kernel(const void* __restrict__ proj, int in_dtype, int row_stride,
+                          const void* __restrict__ q_gamma, const void* __restrict__ k_gamma, int gamma_dtype,
+                          const int* __restrict__ positions, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                          int rot, int table_rows, const int* __restrict__ slot_mapping, void* __restrict__ cache,
+                          void* __restrict__ q_out, int out_dtype, float* __restrict__ gate_out,
+                          int nh, int nkv, int hd, int page_size, float eps, int write_kv) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const size_t row = (size_t)t * row_stride;
+    const int qw = nh * hd, kw = nkv * hd;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < qw; i += blockDim.x) { const float v = rv_load_any(proj, in_dtype, row + i); sq = fmaf(v, v, sq); }
+    for (int i = threadIdx.x; i < kw; i += blockDim.x) { const float v = rv_load_any(proj, in_dtype, row + qw + i); sk = fmaf(v, v, sk); }
+    sq = rv_block_sum(sq, scratch);
+    sk = rv_block_sum(sk, scratch);
+    const float rq = 1.0f / sqrtf(sq / (float)qw + eps), rk = 1.0f / sqrtf(sk / (float)kw + eps);
+    int pos = positions[t];
+    if (pos < 0) pos = 0;
+    if (pos >= table_rows) pos = table_rows - 1;      // the host refuses such positions; never read outside
+    const int half = rot >> 1;
+    const int slot = write_kv ? slot_mapping[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
+    // one item = one element of q or k that is not the second of a rotation pair: i < half (pair with i + half) or i >= rot
+    const int per_head = hd - half;
+    const int n_items = (nh + (write_kv ? nkv : 0)) * per_head;
+    for (int item = threadIdx.x; item < n_items; item += blockDim.x) {
+        const int head = item / per_head;
+        int i = item - head * per_head;
+        const bool paired = i < half;
+        if (!paired) i += half;                        // elements rot .. hd-1 pass unrotated
+        const bool is_q = head < nh;
+        const int col = is_q ? head * hd : (head - nh) * hd;      // within q or within k
+        const size_t src = row + (is_q ? 0 : qw) + col;
+        const void* gamma = is_q ? q_gamma : k_gamma;
+        const float r = is_q ? rq : rk;
+        void* dst;
+        size_t d0;
+        if (is_q) { dst = q_out; d0 = (size_t)t * qw + col; }
+        else {
+            if (slot < 0) continue;
+            dst = cache;
+            d0 = ((((size_t)page * 2) * nkv + (head - nh)) * page_size + off) * hd;
+        }
+        const float raw_a = rv_load_any(proj, in_dtype, src + i);
+        const float a = raw_a * r * rv_load_param(gamma, gamma_dtype, col + i);
+        if (paired) {
+            const float raw_b = rv_load_any(proj, in_dtype, src + i + half);
+            const float b = raw_b * r * rv_load_param(gamma, gamma_dtype, col + i + half);
+            float c = 1.f, s = 0.f;
+            if (cos_t) { c = cos_t[(size_t)pos * half + i]; s = sin_t[(size_t)pos * half + i]; }
+            rv_store_any(dst, out_dtype, d0 + i, a * c - b * s);
+            rv_store_any(dst, out_dtype, d0 + i + half, b * c + a * s);
+            if (!is_q) {                                // the value is the key as projected
+                const size_t v0 = d0 + (size_t)nkv * page_size * hd;
+                rv_store_any(cache, out_dtype, v0 + i, raw_a);
+                rv_store_any(cache, out_dtype, v0 + i + half, raw_b);
+            }
+        } else {
+            rv_store_any(dst, out_dtype, d0 + i, a);
+            if (!is_q) rv_store_any(cache, out_dtype, d0 + (size_t)nkv * page_size * hd + i, raw_a);
+        }
+    }
+    if (gate_out)
+        for (int h = threadIdx.x; h < nh; h += blockDim.x) {
+            const float g = rv_load_any(proj, in_dtype, row + qw + kw + h);
+            gate_out[(size_t)t * nh + h] = 1.0f / (1.0f + expf(-g));
+        }
+}
+
+RV_EXPORT int rv_qk_norm_rope_write(const void* proj, int in_dtype, int row_stride, const void* q_gamma, const void* k_gamma,
+                                    int gamma_dtype, const int* positions, const float* cos_t, const float* sin_t, int rot,
+                                    int table_rows, const int* slot_mapping, void* cache, void* q_out, int out_dtype,
+                                    float* gate_out, int n_tokens, int nh, int nkv, int hd, int page_size, float eps,
+                                    int write_kv, cudaStream_t stream) {
+    if (n_tokens < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || table_rows <= 0) return RV_ERR_BAD_SIZE;
+    if (rot < 0 || rot > hd || (rot & 1)) return RV_ERR_BAD_SIZE;
+    if (row_stride < (nh + nkv) * hd + (gate_out ? nh : 0)) return RV_ERR_BAD_SIZE;
+    if ((in_dtype | gamma_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (n_tokens == 0) return RV_OK;
+    if (!cos_t) rot = 0;
+    RV_LAUNCH_ST = rv_launch(qk_norm_rope_write_kernel, dim3(n_tokens), dim3(256), 0, stream, proj, in_dtype, row_stride, q_gamma,
+                             k_gamma, gamma_dtype, positions, cos_t, sin_t, rot, table_rows, slot_mapping, cache, q_out,
+                             out_dtype, gate_out, nh, nkv, hd, page_size, eps, write_kv);
+    return rv_launch_status();
+}
+
+// ------------------------------------------------------------------ gate, then RMSNorm in equal parts of a row
+// out[t, c] = n(y[t, c] * silu(z[t, c])) * gamma[c], n = RMSNorm over the part of the row that c lies in.
+// Grid (tokens, parts).  z is read from rows of `z_stride` elements (a slice of a wider projection).
+__global__ void __launch_bounds__(256)
+gated_group_rmsnorm_kernel(const float* __restrict__ y, const void* __restrict__ z, int z_dtype, int z_stride,
+                           const void* __restrict__ gamma, int gamma_dtype, void* __restrict__ out, int out_dtype,
+                           int width, int part, float eps) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, c0 = blockIdx.y * part;
+    const size_t yb = (size_t)t * width + c0, zb = (size_t)t * z_stride + c0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        const float v = y[yb + i] * rv_silu(rv_load_any(z, z_dtype, zb + i));
+        ss = fmaf(v, v, ss);
+    }
+    ss = rv_block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)part + eps);
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        const float v = y[yb + i] * rv_silu(rv_load_any(z, z_dtype, zb + i));
+        rv_store_any(out, out_dtype, yb + i, v * r * rv_load_param(gamma, gamma_dtype, c0 + i));
+    }
+}
+
+RV_EXPORT int rv_gated_group_rmsnorm(const float* y, const void* z, int z_dtype, int z_stride, const void* gamma, int gamma_dtype,
+                                     void* out, int out_dtype, int rows, int width, int parts, float eps, cudaStream_t stream) {
+    if (rows < 0 || width <= 0 || parts <= 0 || width % parts || z_stride < width || parts > 65535) return RV_ERR_BAD_SIZE;
+    if ((z_dtype | gamma_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (rows == 0) return RV_OK;
+    const int part = width / parts;
+    RV_LAUNCH_ST = rv_launch(gated_group_rmsnorm_kernel, dim3(rows, parts), dim3(part >= 1024 ? 256 : 128), 0, stream, y, z, z_dtype,
+                             z_stride, gamma, gamma_dtype, out, out_dtype, width, part, eps);
+    return rv_launch_status();
+}

@@ -199,10 +199,12 @@ class CudaKernels:
                                                         c_int(source.shape[0]), c_int(sampled.shape[0]), self._stream())
         _check("late_tokens", st)
 
-    def rmsnorm(self, x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
+    def rmsnorm(self, x: torch.Tensor, gamma: torch.Tensor, eps: float, out_dtype=None) -> torch.Tensor:
         _need(x, "x", dims=2); _need(gamma, "gamma", dims=1)
         if gamma.shape[0] != x.shape[1]:
             raise KernelError(f"rmsnorm: gamma has {gamma.shape[0]} entries for rows of {x.shape[1]}")
+        if out_dtype is not None and out_dtype != x.dtype:      # a float32 stream normalised into the activations' type
+            return self.residual_rmsnorm(x, gamma, eps, None, out_dtype, keep_residual=False)[1]
         out = torch.empty_like(x)
         st = self._lib("elementwise.cu").rv_rmsnorm(
             _ptr(x), _ptr(gamma), c_int(self._dt(gamma, "gamma")), _ptr(out), c_int(x.shape[0]),
@@ -261,15 +263,21 @@ class CudaKernels:
 
     # ------------------------------------------------------------------ attention
     def paged_attention(self, q, cache_layer, meta: AttentionMeta, num_heads, num_kv_heads, head_dim,
-                        scale: float, window: Optional[int]) -> torch.Tensor:
+                        scale: float, window: Optional[int], softcap: Optional[float] = None,
+                        sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Attention of the step's tokens over the paged cache (keys of this step included).
+
+        `softcap`: scaled scores pass c * tanh(s / c); `sinks` (float [heads]): exp(sink) joins each head's
+        softmax denominator; `gate` (float [tokens, heads]): multiplies each head's output.
 
         bfloat16 with a head size that is a multiple of 16 and pages of a power of two go to the
         tensor-core flash kernel (one token per sequence: the decode tiling, keys split over CTAs
         when the batch alone cannot fill the GPU); everything else goes to the plain kernel."""
         page = cache_layer.shape[3]
-        if q.dtype != torch.bfloat16 or head_dim % 16 or head_dim > 256 or (page & (page - 1)):
-            return self.paged_attention_plain(q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window)
+        extras = softcap is not None or sinks is not None or gate is not None
+        if extras or q.dtype != torch.bfloat16 or head_dim % 16 or head_dim > 256 or (page & (page - 1)):
+            return self.paged_attention_plain(q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window,
+                                              softcap, sinks, gate)
         out = torch.empty_like(q)
         group = num_heads // num_kv_heads
         if self.TCGEN05_ATTENTION and meta.max_q_len >= self.TCGEN05_ATTENTION_MIN_TOKENS and head_dim in (64, 128) \
@@ -424,16 +432,29 @@ class CudaKernels:
         _check("attention_tcgen05", st)
         return out
 
-    def paged_attention_plain(self, q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window):
+    def paged_attention_plain(self, q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window,
+                              softcap=None, sinks=None, gate=None):
         _need(q, "q", dims=2); _need(cache_layer, "cache_layer", q.dtype, 5)
+        self._check_attention_extras(q, num_heads, sinks, gate)
         out = torch.empty_like(q)
         st = self._lib("attention_ref.cu").rv_paged_attention_ref(
             _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens),
             _ptr(meta.token_seq), _ptr(out), c_int(q.shape[0]), c_int(num_heads), c_int(num_kv_heads),
             c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks), c_float(scale),
-            c_int(window or 0), c_int(self._dt(q, "q")), self._stream())
+            c_int(window or 0), c_float(softcap or 0.0), _ptr(sinks), _ptr(gate), c_int(self._dt(q, "q")), self._stream())
         _check("paged_attention_plain", st)
         return out
+
+    @staticmethod
+    def _check_attention_extras(q, num_heads, sinks, gate):
+        if sinks is not None:
+            _need(sinks, "sinks", torch.float32, 1)
+            if sinks.shape[0] != num_heads:
+                raise KernelError(f"attention: {sinks.shape[0]} sinks for {num_heads} heads")
+        if gate is not None:
+            _need(gate, "gate", torch.float32, 2)
+            if tuple(gate.shape) != (q.shape[0], num_heads):
+                raise KernelError(f"attention: gate of shape {tuple(gate.shape)} for {q.shape[0]} tokens of {num_heads} heads")
 
     # ------------------------------------------------------------------ linear layers
     def linear(self, x, weight, bias=None, residual=None, out_dtype=None, norm=None) -> torch.Tensor:
@@ -455,7 +476,7 @@ class CudaKernels:
                     and (residual is None or (residual.dtype == torch.bfloat16 and out_dtype == torch.bfloat16)))
             if fuse:
                 return self.linear_decode(x, weight, bias, residual, out_dtype, norm=norm)
-            x = self.rmsnorm(x, *norm)
+            x = self.rmsnorm(x, *norm, out_dtype=weight.dtype if x.dtype == torch.float32 else None)
         if weight.dtype == torch.float32:
             xf = x if x.dtype == torch.float32 else x.float()
             rf = None
@@ -781,6 +802,149 @@ class CudaKernels:
                 and K % 8 == 0 and weight.shape[0] % 2 == 0:
             return self.linear_tcgen05(x, weight, gated=True)
         return self.silu_mul(self.linear(x, weight))
+
+    # ------------------------------------------------------------------ output-norm layers, gated attention, state-space mixer
+    def residual_rmsnorm(self, y, gamma, eps: float, residual: Optional[torch.Tensor], rounded_dtype=None,
+                         keep_residual: bool = True):
+        """r = residual + y / sqrt(mean(y^2) + eps) * gamma in float32 (residual None: zero).  Returns
+        (r as float32 [rows, cols] or None without `keep_residual`, r rounded to `rounded_dtype` or None).
+        `residual` is updated in place when given."""
+        _need(y, "y", dims=2); _need(gamma, "gamma", dims=1)
+        rows, cols = y.shape
+        if gamma.shape[0] != cols:
+            raise KernelError(f"residual_rmsnorm: gamma has {gamma.shape[0]} entries for rows of {cols}")
+        if residual is not None:
+            _need(residual, "residual", torch.float32, 2)
+            if residual.shape != y.shape:
+                raise KernelError(f"residual_rmsnorm: residual {tuple(residual.shape)} against rows {tuple(y.shape)}")
+        res_out = None
+        if keep_residual:
+            res_out = residual if residual is not None else torch.empty((rows, cols), dtype=torch.float32, device=y.device)
+        rounded = None
+        if rounded_dtype is not None and not (rounded_dtype == torch.float32 and keep_residual):
+            rounded = torch.empty((rows, cols), dtype=rounded_dtype, device=y.device)
+        st = self._lib("rowops.cu").rv_residual_rmsnorm(
+            _ptr(y), c_int(self._dt(y, "y")), _ptr(gamma), c_int(self._dt(gamma, "gamma")), _ptr(residual), _ptr(res_out),
+            _ptr(rounded), c_int(_DT[rounded_dtype] if rounded is not None else 0), c_int(rows), c_int(cols), c_float(eps),
+            self._stream())
+        _check("residual_rmsnorm", st)
+        if rounded is None and rounded_dtype == torch.float32:
+            rounded = res_out
+        return res_out, rounded
+
+    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+    def act_mul(self, gate_up: torch.Tensor, activation: str, out_dtype=None) -> torch.Tensor:
+        """rows [gate | up] -> act(gate) * up, computed in float."""
+        _need(gate_up, "gate_up", dims=2)
+        if activation not in self.ACTIVATIONS:
+            raise KernelError(f"act_mul: activation {activation!r} is not known ({', '.join(self.ACTIVATIONS)})")
+        inter = gate_up.shape[1] // 2
+        if inter * 2 != gate_up.shape[1]:
+            raise KernelError(f"act_mul: row width {gate_up.shape[1]} is odd")
+        out = torch.empty((gate_up.shape[0], inter), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
+        st = self._lib("rowops.cu").rv_act_mul(_ptr(gate_up), c_int(self._dt(gate_up, "gate_up")), _ptr(out), c_int(self._dt(out, "out")),
+                                               c_int(gate_up.shape[0]), c_int(inter), c_int(self.ACTIVATIONS[activation]), self._stream())
+        _check("act_mul", st)
+        return out
+
+    def gate_up_act(self, x, weight, activation: str, out_dtype=None) -> torch.Tensor:
+        """act(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu].  SiLU takes the fused kernels of `gate_up_silu`; other
+        activations run the product with a float32 result and the activation kernel, which rounds once."""
+        if activation == "silu" and (out_dtype is None or out_dtype == x.dtype):
+            return self.gate_up_silu(x, weight)
+        return self.act_mul(self.linear(x, weight, out_dtype=torch.float32), activation, out_dtype or x.dtype)
+
+    def qk_norm_rope_cache_write(self, proj, q_gamma, k_gamma, eps: float, positions, cos, sin, slot_mapping, cache_layer,
+                                 num_heads, num_kv_heads, head_dim, out_dtype, with_gate: bool = False, write_kv: bool = True):
+        """proj rows [q | k | gate logits]: q and k are each RMS-normalised over their whole part of the row
+        (weights `q_gamma`, `k_gamma` of those widths), the leading 2 * cos.shape[1] elements of every head are
+        rotated, k goes into the token's cache slot as the key and, as projected, as the value.
+        Returns (q [T, heads * head_dim] in `out_dtype`, sigmoid(gate logits) float [T, heads] or None)."""
+        _need(proj, "proj", dims=2); _need(positions, "positions", torch.int32, 1)
+        _need(q_gamma, "q_gamma", dims=1); _need(k_gamma, "k_gamma", q_gamma.dtype, 1)
+        T = proj.shape[0]
+        qw, kw = num_heads * head_dim, num_kv_heads * head_dim
+        if proj.shape[1] != qw + kw + (num_heads if with_gate else 0):
+            raise KernelError(f"qk_norm_rope_cache_write: rows of {proj.shape[1]} columns, expected {qw} + {kw}"
+                              + (f" + {num_heads}" if with_gate else ""))
+        if q_gamma.shape[0] != qw or k_gamma.shape[0] != kw:
+            raise KernelError("qk_norm_rope_cache_write: the norm weights do not have the widths of q and k")
+        rot, table_rows = 0, 1
+        if cos is not None:
+            _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+            rot, table_rows = 2 * cos.shape[1], cos.shape[0]
+            if not 0 < rot <= head_dim or sin.shape != cos.shape:
+                raise KernelError(f"qk_norm_rope_cache_write: cos/sin tables must be [rows, rotary_dim/2] with rotary_dim <= {head_dim}")
+        if write_kv:
+            _need(cache_layer, "cache_layer", out_dtype, 5); _need(slot_mapping, "slot_mapping", torch.int32, 1)
+            if tuple(cache_layer.shape[1:3]) != (2, num_kv_heads) or cache_layer.shape[4] != head_dim:
+                raise KernelError(f"qk_norm_rope_cache_write: cache layer of shape {tuple(cache_layer.shape)} does not "
+                                  f"fit {num_kv_heads} kv heads of {head_dim}")
+        q = torch.empty((T, qw), dtype=out_dtype, device=proj.device)
+        gate = torch.empty((T, num_heads), dtype=torch.float32, device=proj.device) if with_gate else None
+        st = self._lib("rowops.cu").rv_qk_norm_rope_write(
+            _ptr(proj), c_int(self._dt(proj, "proj")), c_int(proj.shape[1]), _ptr(q_gamma), _ptr(k_gamma),
+            c_int(self._dt(q_gamma, "q_gamma")), _ptr(positions), _ptr(cos), _ptr(sin), c_int(rot), c_int(table_rows),
+            _ptr(slot_mapping if write_kv else None), _ptr(cache_layer if write_kv else None), _ptr(q), c_int(_DT[out_dtype]),
+            _ptr(gate), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+            c_int(cache_layer.shape[3] if write_kv else 1), c_float(eps), c_int(1 if write_kv else 0), self._stream())
+        _check("qk_norm_rope_cache_write", st)
+        return q, gate
+
+    def causal_conv_silu(self, proj, col0: int, channels: int, weight, bias, token_seq, cu_seqlens, state_slots, state,
+                         conv_off: int, out_dtype) -> torch.Tensor:
+        """silu(causal convolution per channel) of columns col0 .. col0 + channels of `proj`, continued from and
+        leaving behind each request's last taps - 1 inputs in `state` (float [slots, floats], at `conv_off`)."""
+        _need(proj, "proj", dims=2); _need(weight, "weight", dims=2); _need(state, "state", torch.float32, 2)
+        if weight.shape[0] != channels or (bias is not None and (bias.shape != (channels,) or bias.dtype != weight.dtype)):
+            raise KernelError("causal_conv_silu: taps and bias do not fit the channels")
+        T, taps = proj.shape[0], weight.shape[1]
+        if conv_off + (taps - 1) * channels > state.shape[1]:
+            raise KernelError("causal_conv_silu: the state rows are too short for the convolution's inputs")
+        out = torch.empty((T, channels), dtype=out_dtype, device=proj.device)
+        st = self._lib("ssm.cu").rv_causal_conv_silu(
+            _ptr(proj), c_int(self._dt(proj, "proj")), c_int(proj.shape[1]), c_int(col0), _ptr(weight), _ptr(bias),
+            c_int(self._dt(weight, "weight")), _ptr(token_seq), _ptr(cu_seqlens), _ptr(state_slots), _ptr(state),
+            ctypes.c_longlong(state.shape[1]), ctypes.c_longlong(conv_off), _ptr(out), c_int(_DT[out_dtype]), c_int(T),
+            c_int(state_slots.shape[0]), c_int(channels), c_int(taps), self._stream())
+        _check("causal_conv_silu", st)
+        COUNTERS['launches'] += 1 if taps > 1 else 0
+        return out
+
+    def ssm_scan(self, xbc, proj, dt_col0: int, dt_bias, a_log, d_skip, cu_seqlens, state_slots, state, heads: int,
+                 head_dim: int, state_size: int, groups: int) -> torch.Tensor:
+        """The selective-state recurrence over the step's tokens, continued from and leaving behind each request's
+        S in `state` (float [slots, floats], [heads][N][P] at offset 0).  xbc rows: [x | B | C]; raw dt is read
+        from columns dt_col0 .. of `proj`.  Returns y float32 [T, heads * head_dim]."""
+        _need(xbc, "xbc", dims=2); _need(proj, "proj", dims=2); _need(state, "state", torch.float32, 2)
+        for name, p in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
+            _need(p, name, dt_bias.dtype, 1)
+            if p.shape[0] != heads:
+                raise KernelError(f"ssm_scan: {name} has {p.shape[0]} entries for {heads} heads")
+        if state.shape[1] < heads * state_size * head_dim:
+            raise KernelError("ssm_scan: the state rows are too short")
+        y = torch.empty((xbc.shape[0], heads * head_dim), dtype=torch.float32, device=xbc.device)
+        st = self._lib("ssm.cu").rv_ssm_scan(
+            _ptr(xbc), c_int(self._dt(xbc, "xbc")), c_int(xbc.shape[1]), _ptr(proj), c_int(self._dt(proj, "proj")),
+            c_int(proj.shape[1]), c_int(dt_col0), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), c_int(self._dt(dt_bias, "dt_bias")),
+            _ptr(cu_seqlens), _ptr(state_slots), _ptr(state), ctypes.c_longlong(state.shape[1]), _ptr(y),
+            c_int(state_slots.shape[0]), c_int(heads), c_int(head_dim), c_int(state_size), c_int(groups), self._stream())
+        _check("ssm_scan", st)
+        return y
+
+    def gated_group_rmsnorm(self, y, proj, gamma, eps: float, parts: int, out_dtype) -> torch.Tensor:
+        """(y * silu(z)) RMS-normalised in `parts` equal parts of a row, times gamma; z = the leading columns of `proj`."""
+        _need(y, "y", torch.float32, 2); _need(proj, "proj", dims=2); _need(gamma, "gamma", dims=1)
+        rows, width = y.shape
+        if gamma.shape[0] != width or proj.shape[0] != rows or proj.shape[1] < width or width % parts:
+            raise KernelError("gated_group_rmsnorm: shapes of y, z, gamma and the parts do not agree")
+        out = torch.empty((rows, width), dtype=out_dtype, device=y.device)
+        st = self._lib("rowops.cu").rv_gated_group_rmsnorm(
+            _ptr(y), _ptr(proj), c_int(self._dt(proj, "proj")), c_int(proj.shape[1]), _ptr(gamma), c_int(self._dt(gamma, "gamma")),
+            _ptr(out), c_int(_DT[out_dtype]), c_int(rows), c_int(width), c_int(parts), c_float(eps), self._stream())
+        _check("gated_group_rmsnorm", st)
+        return out
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature=None, top_k=None, top_p=None, seeds=None, draw_index=None) -> torch.Tensor:

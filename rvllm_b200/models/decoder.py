@@ -128,6 +128,9 @@ class DecoderModel:
             x = pe.on_embeddings(x, ctx)
         for hook in self.embedding_hooks:
             x = hook(x, ctx)
+        ctx.extras["activation_dtype"] = self.dtype
+        if self.spec.residual_dtype == "float32" and x.dtype != torch.float32:
+            x = x.float()              # the stream between the layers stays in 32 bits; blocks round a copy for their products
         for e in self.spec.run_order:
             x = self.layers[e.layer].block(x, ctx, caches.view(e.cache), e.writes_cache)
         return x

@@ -5,4 +5,6 @@ from .norm import RMSNorm
 from .rope import RotaryEncoding, inverse_frequencies
 from .attention import PagedAttention
 from .mlp import GatedMLP
-from .block import PreNormResidualBlock
+from .block import PreNormResidualBlock, OutputNormResidualBlock
+from .sink_attention import GatedSinkAttention
+from .mamba2 import Mamba2Mixer

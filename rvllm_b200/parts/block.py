@@ -10,6 +10,8 @@ few rows); the block then hands it the unnormalised x.  A norm offers this throu
 parts and norms without these attributes are combined the plain way."""
 from __future__ import annotations
 
+import torch
+
 from .base import BLOCKS
 
 
@@ -42,3 +44,59 @@ class PreNormResidualBlock:
 
 
 BLOCKS.register("prenorm_residual", PreNormResidualBlock)
+
+
+class OutputNormResidualBlock:
+    """`output_norm_residual`: x + norm(mixer(x)), then + norm(feed_forward(x)); the sublayers read the stream
+    itself and the norm acts on what they return.  A layer may have no feed-forward.
+
+    The stream x is float32 whatever the engine's type (`ModelSpec.residual_dtype`): the norm, the sum and
+    the stream stay in 32 bits, and the kernel that adds also leaves the copy of the new stream in the
+    activations' type that the next sublayer's products read.  The copy travels beside the stream in
+    `ctx.extras`; a block that finds none (the first layer) makes one.  Sublayers are asked for a float32
+    result (`out_dtype`), so that what is normalised was rounded nowhere after its last product."""
+    ROLES = ("mixer", "mixer_norm")
+    OPTIONAL = ("feed_forward", "feed_forward_norm")
+    KEY = "rounded_stream"
+
+    def __init__(self, parts):
+        from ..errors import ConfigError
+        names = set(parts)
+        if not set(self.ROLES) <= names or not names <= set(self.ROLES + self.OPTIONAL) or \
+                (("feed_forward" in names) != ("feed_forward_norm" in names)):
+            raise ConfigError(f"the output-norm residual block arranges {', '.join(self.ROLES)} and, together, "
+                              f"{', '.join(self.OPTIONAL)}; got {', '.join(sorted(parts))}")
+        self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
+        self.feed_forward, self.feed_forward_norm = parts.get("feed_forward"), parts.get("feed_forward_norm")
+        for n in (self.mixer_norm, self.feed_forward_norm):
+            if n is not None and not hasattr(n, "as_rms"):
+                raise ConfigError("the output-norm residual block needs norms that offer `as_rms()` (an RMSNorm)")
+
+    def _rounded(self, x, ctx, dtype):
+        if dtype == torch.float32:
+            return x
+        kept = ctx.extras.get(self.KEY)
+        if kept is not None and kept[0] is x:
+            return kept[1]
+        return x.to(dtype)
+
+    def _add(self, x, y, norm, ctx, dtype):
+        gamma, eps = norm.as_rms()
+        x, h = ctx.kernels.residual_rmsnorm(y, gamma, eps, x, dtype)
+        ctx.extras[self.KEY] = (x, h)
+        return x
+
+    def __call__(self, x, ctx, cache, write_cache=True):
+        dtype = ctx.extras.get("activation_dtype", x.dtype)
+        if x.dtype != torch.float32:
+            x = x.float()
+        h = self._rounded(x, ctx, dtype)
+        x = self._add(x, self.mixer(h, ctx, cache, residual=None, write_cache=write_cache, out_dtype=torch.float32),
+                      self.mixer_norm, ctx, dtype)
+        if self.feed_forward is not None:
+            h = self._rounded(x, ctx, dtype)
+            x = self._add(x, self.feed_forward(h, ctx, residual=None, out_dtype=torch.float32), self.feed_forward_norm, ctx, dtype)
+        return x
+
+
+BLOCKS.register("output_norm_residual", OutputNormResidualBlock)

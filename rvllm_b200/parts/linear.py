@@ -13,8 +13,11 @@ class Linear(Part):
     dimension (q, k, v; gate, up): the stacked product is one GEMM
     (fusing after v3/crates/rvllm-loader/src/load_multiformat.rs:372-407, 445-477)."""
 
-    def __init__(self, in_features: int, out_features: Sequence[int], names: Sequence[str], bias: bool = False):
+    def __init__(self, in_features: int, out_features: Sequence[int], names: Sequence[str], bias: bool = False,
+                 suffix: str = ".weight"):
+        """`suffix` follows a matrix's name in the checkpoint (".weight" in most; "" where the name is the tensor)."""
         assert len(out_features) == len(names)
+        self.suffix = suffix
         self.in_features = in_features
         self.out_features = list(out_features)
         self.names = list(names)
@@ -25,13 +28,13 @@ class Linear(Part):
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {}
         for name, n in zip(self.names, self.out_features):
-            specs[f"{name}.weight"] = TensorSpec((n, self.in_features), "matrix")
+            specs[f"{name}{self.suffix}"] = TensorSpec((n, self.in_features), "matrix")
             if self.has_bias:
                 specs[f"{name}.bias"] = TensorSpec((n,), "bias")
         return specs
 
     def bind(self, get) -> None:
-        ws = [get(f"{n}.weight") for n in self.names]
+        ws = [get(f"{n}{self.suffix}") for n in self.names]
         # matrices stored in different precisions are brought to the widest one
         dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
         self.weight = (ws[0].to(dt) if len(ws) == 1 else torch.cat([w.to(dt) for w in ws], dim=0)).contiguous()

@@ -10,15 +10,18 @@ from .base import NORMS, Part, TensorSpec
 
 
 class RMSNorm(Part):
-    def __init__(self, size: int, eps: float):
-        self.size, self.eps = size, eps
+    """`tensor` is the name of the weight below the part's prefix ("weight" in most checkpoints; "" where the
+    prefix itself names the tensor)."""
+
+    def __init__(self, size: int, eps: float, tensor: str = "weight"):
+        self.size, self.eps, self.tensor = size, eps, tensor
         self.weight = None
 
     def tensor_specs(self):
-        return {"weight": TensorSpec((self.size,), "norm")}
+        return {self.tensor: TensorSpec((self.size,), "norm")}
 
     def bind(self, get):
-        self.weight = get("weight")
+        self.weight = get(self.tensor)
 
     def __call__(self, x, ctx):
         return ctx.kernels.rmsnorm(x, self.weight, self.eps)

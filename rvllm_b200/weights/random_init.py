@@ -1,7 +1,8 @@
 """Random-weights mode: write a model folder (config.json, model.safetensors) from a
 configuration and a seed.
 
-Distributions: matrices N(0, 0.02), norm weights 1 + N(0, 0.1), biases N(0, 0.02).  The
+Distributions: matrices N(0, 0.02), norm weights 1 + N(0, 0.1), biases N(0, 0.02), taps of a
+short convolution N(0, 0.3).  The
 reference has no such mode (its benchmarks run on uninitialised caches,
 v3/crates/rvllm-runtime/src/bring_up.rs:395-404); these are the distributions this
 project's benchmark configurations name.  Tensors are drawn in sorted name order from one
@@ -17,7 +18,7 @@ import torch
 
 from .safetensors_io import write_safetensors
 
-INIT_STD = {"matrix": (0.0, 0.02), "norm": (1.0, 0.1), "bias": (0.0, 0.02)}
+INIT_STD = {"matrix": (0.0, 0.02), "norm": (1.0, 0.1), "bias": (0.0, 0.02), "conv_taps": (0.0, 0.3)}
 
 
 def random_tensors(tensor_specs: Dict[str, "TensorSpec"], seed: int, dtype: torch.dtype,

@@ -22,10 +22,94 @@ class EmulatedKernels:
             if j >= 0:
                 token_ids[int(cu_seqlens[i])] = sampled[j]
 
-    def rmsnorm(self, x, gamma, eps):
+    def rmsnorm(self, x, gamma, eps, out_dtype=None):
         xf = x.float()
         r = 1.0 / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps)
-        return (xf * r * gamma.float()).to(x.dtype)
+        return (xf * r * gamma.float()).to(out_dtype or x.dtype)
+
+    def residual_rmsnorm(self, y, gamma, eps, residual, rounded_dtype=None, keep_residual=True):
+        r = self.rmsnorm(y.float(), gamma, eps)
+        if residual is not None:
+            residual += r
+            r = residual
+        return (r if keep_residual else None), (r.to(rounded_dtype) if rounded_dtype is not None else None)
+
+    def act_mul(self, gate_up, activation, out_dtype=None):
+        inter = gate_up.shape[1] // 2
+        g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+        if activation == "silu":
+            a = g / (1.0 + torch.exp(-g))
+        else:
+            a = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
+        return (a * u).to(out_dtype or gate_up.dtype)
+
+    def gate_up_act(self, x, weight, activation, out_dtype=None):
+        return self.act_mul(self.linear(x, weight, out_dtype=torch.float32), activation, out_dtype or x.dtype)
+
+    def qk_norm_rope_cache_write(self, proj, q_gamma, k_gamma, eps, positions, cos, sin, slot_mapping, cache_layer,
+                                 num_heads, num_kv_heads, head_dim, out_dtype, with_gate=False, write_kv=True):
+        T = proj.shape[0]
+        qw, kw = num_heads * head_dim, num_kv_heads * head_dim
+        x = proj.float()
+        q = self.rmsnorm(x[:, :qw], q_gamma, eps)
+        kraw = x[:, qw:qw + kw]
+        kn = self.rmsnorm(kraw, k_gamma, eps)
+        stacked = torch.cat([q, kn, kraw], dim=1)         # the rotation below leaves the third part alone
+        qo = self.rope_cache_write(stacked, None, positions, cos, sin, slot_mapping, cache_layer, num_heads, num_kv_heads,
+                                   head_dim, write_kv=write_kv, out_dtype=out_dtype) if write_kv else \
+            self.rope_cache_write(q.contiguous(), None, positions, cos, sin, None, None, num_heads, num_kv_heads, head_dim,
+                                  write_kv=False, out_dtype=out_dtype)
+        gate = torch.sigmoid(x[:, qw + kw:]) if with_gate else None
+        return qo, gate
+
+    def causal_conv_silu(self, proj, col0, channels, weight, bias, token_seq, cu_seqlens, state_slots, state, conv_off, out_dtype):
+        taps = weight.shape[1]
+        u = proj[:, col0:col0 + channels].float()
+        out = torch.zeros_like(u)
+        cu = cu_seqlens.tolist()
+        for s, slot in enumerate(state_slots.tolist()):
+            if slot < 0:
+                continue
+            hist = state[slot, conv_off:conv_off + (taps - 1) * channels].view(taps - 1, channels)
+            seq = torch.cat([hist, u[cu[s]:cu[s + 1]]], dim=0)
+            n = cu[s + 1] - cu[s]
+            acc = torch.zeros((n, channels))
+            for j in range(taps):
+                acc = acc + seq[j:j + n] * weight[:, j].float()[None, :]
+            if bias is not None:
+                acc = acc + bias.float()[None, :]
+            out[cu[s]:cu[s + 1]] = acc / (1.0 + torch.exp(-acc))
+            hist.copy_(seq[n:n + taps - 1].clone())
+        return out.to(out_dtype)
+
+    def ssm_scan(self, xbc, proj, dt_col0, dt_bias, a_log, d_skip, cu_seqlens, state_slots, state, heads, head_dim,
+                 state_size, groups):
+        T = xbc.shape[0]
+        inner, P, N = heads * head_dim, head_dim, state_size
+        xf = xbc.float()
+        y = torch.zeros((T, inner))
+        cu = cu_seqlens.tolist()
+        for s, slot in enumerate(state_slots.tolist()):
+            if slot < 0:
+                continue
+            S = state[slot, :heads * N * P].view(heads, N, P)
+            for t in range(cu[s], cu[s + 1]):
+                dt = torch.nn.functional.softplus(proj[t, dt_col0:dt_col0 + heads].float() + dt_bias.float(), threshold=20.0)
+                for h in range(heads):
+                    g = h // (heads // groups)
+                    x = xf[t, h * P:(h + 1) * P]
+                    B = xf[t, inner + g * N:inner + (g + 1) * N]
+                    C = xf[t, inner + groups * N + g * N:inner + groups * N + (g + 1) * N]
+                    S[h] = torch.exp(-torch.exp(a_log[h].float()) * dt[h]) * S[h] + dt[h] * B[:, None] * x[None, :]
+                    y[t, h * P:(h + 1) * P] = S[h].t() @ C + d_skip[h].float() * x
+        return y
+
+    def gated_group_rmsnorm(self, y, proj, gamma, eps, parts, out_dtype):
+        rows, width = y.shape
+        z = proj[:, :width].float()
+        v = (y * (z / (1.0 + torch.exp(-z)))).view(rows, parts, width // parts)
+        v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+        return (v.reshape(rows, width) * gamma.float()).to(out_dtype)
 
     def silu_mul(self, gate_up):
         inter = gate_up.shape[1] // 2
@@ -68,7 +152,8 @@ class EmulatedKernels:
         return self.rope_cache_write(self.linear(x, weight, norm=norm), bias, positions, cos, sin, slot_mapping, cache_layer,
                                      num_heads, num_kv_heads, head_dim)
 
-    def paged_attention(self, q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window):
+    def paged_attention(self, q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window,
+                        softcap=None, sinks=None, gate=None):
         T = q.shape[0]
         ps = cache_layer.shape[3]
         out = torch.zeros_like(q).view(T, num_heads, head_dim)
@@ -92,8 +177,17 @@ class EmulatedKernels:
                     g = h * num_kv_heads // num_heads
                     K = cache_layer[pages, 0, g, offs, :].float()
                     V = cache_layer[pages, 1, g, offs, :].float()
-                    p = torch.softmax((K @ qv[t, h]) * scale, 0)
-                    out[t, h] = (p @ V).to(q.dtype)
+                    sc = (K @ qv[t, h]) * scale
+                    if softcap is not None:
+                        sc = softcap * torch.tanh(sc / softcap)
+                    if sinks is not None:
+                        p = torch.softmax(torch.cat([sc, sinks[h:h + 1].float()]), 0)[:-1]
+                    else:
+                        p = torch.softmax(sc, 0)
+                    o = p @ V
+                    if gate is not None:
+                        o = o * gate[t, h]
+                    out[t, h] = o.to(q.dtype)
         return out.view(T, num_heads * head_dim)
 
     def linear(self, x, weight, bias=None, residual=None, out_dtype=None, norm=None):
