@@ -65,6 +65,14 @@ class TufiraxConfig:
     def architecture(self) -> str:
         return self.ARCHITECTURE
 
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def hidden_size(self) -> int:
+        return self.width
+
     # ---- reading -------------------------------------------------------------------------------
     @classmethod
     def from_dict(cls, obj: Dict[str, Any], where: str = "config.json") -> "TufiraxConfig":

@@ -76,7 +76,36 @@ struct FlashParams {
     int num_splits;
     int row_tiles;                 // row tiles per sequence the grid provides
     int q_filter;                  // 0: every sequence, 1: only q_len == 1, 2: only q_len > 1
+    // options (rv_flash_attention_ex, rv_flash_decode_tma_ex): a capped score c tanh(s / c), a sink per head in the
+    // softmax denominator, a gate per (token, head) on the output
+    float cap_log2e;               // c log2(e); 0: no cap
+    float scale_over_cap;          // scale / c
+    const float* sinks;            // [nh] or null
+    const float* gate;             // [n_tokens, nh] or null
 };
+
+// The score in units of log2: scale * raw, or with a cap c: c * tanh(scale * raw / c) (tanh as 1 - 2 / (e^2x + 1)).
+__device__ __forceinline__ float flash_score(float raw, const FlashParams& p) {
+    if (p.cap_log2e > 0.f) {
+        const float e = exp2f(raw * p.scale_over_cap * 2.885390081777927f);
+        return p.cap_log2e * (1.f - __fdividef(2.f, e + 1.f));
+    }
+    return raw * p.scale_log2e;
+}
+// What the unnormalised sum of a row is multiplied by at the end: 1 / l; with a sink exp(sink) joins the
+// denominator (m, l in units of log2 as the kernels keep them; m = -inf when no key was seen); a gate multiplies.
+__device__ __forceinline__ float flash_final(float m, float l, const float* sinks, const float* gate, size_t row_out, int head) {
+    float num = 1.f, den = l;
+    if (sinks) {
+        const float sk = sinks[head] * 1.4426950408889634f;
+        const float m_new = fmaxf(m, sk);
+        num = exp2f(m - m_new);
+        den = l * num + exp2f(sk - m_new);
+    }
+    float inv = den > 0.f ? num / den : 0.f;
+    if (gate) inv *= gate[row_out];
+    return inv;
+}
 
 template <int WARPS_M, int WARPS_N, int NSTAGES>
 __global__ void __launch_bounds__(WARPS_M * WARPS_N * 32)
@@ -227,7 +256,7 @@ flash_paged_kernel(const FlashParams p) {
                 const int i = e >> 1;
                 const int key = key0 + n * 8 + (e & 1);
                 const bool see = key <= pos[i] && key >= lo[i];
-                const float v = see ? s[n][e] * p.scale_log2e : -INFINITY;
+                const float v = see ? flash_score(s[n][e], p) : -INFINITY;
                 s[n][e] = v;
                 m_tile[i] = fmaxf(m_tile[i], v);
             }
@@ -328,7 +357,7 @@ flash_paged_kernel(const FlashParams p) {
             const int t = rr / G;
             const size_t row_out = (size_t)(q_start + t) * p.nh + kvh * G + (rr - t * G);
             if (p.num_splits == 1) {
-                p.out[row_out * HD + d] = __float2bfloat16_rn(acc * (l_all > 0.f ? 1.f / l_all : 0.f));
+                p.out[row_out * HD + d] = __float2bfloat16_rn(acc * flash_final(m_all, l_all, p.sinks, p.gate, row_out, kvh * G + (rr - t * G)));
             } else {
                 const size_t prow = (size_t)split * p.n_tokens * p.nh + row_out;
                 p.part_o[prow * HD + d] = acc;
@@ -343,7 +372,7 @@ flash_paged_kernel(const FlashParams p) {
         if (r[i] >= rows_total) continue;
         const size_t row_out = (size_t)tok[i] * p.nh + head[i];
         if (p.num_splits == 1) {
-            const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+            const float inv = flash_final(m_run[i], l_run[i], p.sinks, p.gate, row_out, head[i]);
             __nv_bfloat16* dst = p.out + row_out * HD + tq * 2;
 #pragma unroll
             for (int n = 0; n < HD / 8; ++n)
@@ -395,7 +424,8 @@ __device__ __forceinline__ float merge_splits(const float* __restrict__ part_o, 
 
 // The same for four neighbouring elements d .. d + 3 (d a multiple of 4), every split's loads in flight together.
 __device__ __forceinline__ float4 merge_splits4(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                                size_t row, size_t rows, int num_splits, int d) {
+                                                size_t row, size_t rows, int num_splits, int d,
+                                                const float* sinks = nullptr, const float* gate = nullptr, int nh = 1) {
     float m_run = -INFINITY, l_run = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s0 = 0; s0 < num_splits; s0 += 8) {
@@ -425,7 +455,7 @@ __device__ __forceinline__ float4 merge_splits4(const float* __restrict__ part_o
         }
         m_run = m_new;
     }
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    const float inv = flash_final(m_run, l_run, sinks, gate, row, (int)(row % (size_t)nh));
     return make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
 }
 
@@ -434,13 +464,14 @@ __device__ __forceinline__ float4 merge_splits4(const float* __restrict__ part_o
 #define COMBINE_TPR (HEAD_DIM / 4)                 // threads per row
 #define COMBINE_ROWS (128 / COMBINE_TPR)           // rows per block
 __global__ void flash_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                     __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+                                     __nv_bfloat16* __restrict__ out, int rows, int num_splits,
+                                     const float* __restrict__ sinks, const float* __restrict__ gate, int nh) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     const int r = threadIdx.x / COMBINE_TPR, d = (threadIdx.x - r * COMBINE_TPR) * 4;
     const int row = blockIdx.x * COMBINE_ROWS + r;
     if (r >= COMBINE_ROWS || row >= rows) return;
-    const float4 v = merge_splits4(part_o, part_ml, (size_t)row, (size_t)rows, num_splits, d);
+    const float4 v = merge_splits4(part_o, part_ml, (size_t)row, (size_t)rows, num_splits, d, sinks, gate, nh);
     uint2 o2;
     o2.x = pack_bf16(v.x, v.y);
     o2.y = pack_bf16(v.z, v.w);
@@ -643,7 +674,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FlashP
                     const int i = e >> 1;
                     const int key = key0 + n * 8 + (e & 1);
                     const bool see = key <= pos[i] && key >= lo[i];
-                    const float v = see ? s[n][e] * p.scale_log2e : -INFINITY;
+                    const float v = see ? flash_score(s[n][e], p) : -INFINITY;
                     s[n][e] = v;
                     m_tile[i] = fmaxf(m_tile[i], v);
                 }
@@ -737,7 +768,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FlashP
                 const int t = rr / G;
                 const size_t row_out = (size_t)(q_start + t) * p.nh + kvh * G + (rr - t * G);
                 if (p.num_splits == 1) {
-                    p.out[row_out * HD + d] = __float2bfloat16_rn(acc * (l_all > 0.f ? 1.f / l_all : 0.f));
+                    p.out[row_out * HD + d] = __float2bfloat16_rn(acc * flash_final(m_all, l_all, p.sinks, p.gate, row_out, kvh * G + (rr - t * G)));
                 } else {
                     const size_t prow = (size_t)split * p.n_tokens * p.nh + row_out;
                     p.part_o[prow * HD + d] = acc;
@@ -1460,10 +1491,13 @@ RV_EXPORT long long rv_flash_scratch_floats(int n_tokens, int nh, int num_splits
 // mode 0: prefill / mixed tiling (64 rows per CTA); mode 1: decode tiling (16 rows, warps split
 // the keys), for steps in which the selected sequences bring one token each.
 // scratch: float buffer of rv_flash_scratch_floats(...) elements when num_splits > 1.
-RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* block_tables, const int* cu_seqlens,
-                                 const int* ctx_lens, void* out, float* scratch, int n_tokens, int num_seqs,
-                                 int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
-                                 int mode, int max_q_len, int num_splits, int q_filter, cudaStream_t stream) {
+// `softcap` > 0: scaled scores pass softcap * tanh(s / softcap); `sinks` (float [nh]): exp(sink) joins each head's
+// softmax denominator; `gate` (float [n_tokens, nh]): multiplies each head's output.  Null / 0: absent.
+RV_EXPORT int rv_flash_attention_ex(const void* q, const void* cache, const int* block_tables, const int* cu_seqlens,
+                                    const int* ctx_lens, void* out, float* scratch, int n_tokens, int num_seqs,
+                                    int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
+                                    int mode, int max_q_len, int num_splits, int q_filter, float softcap,
+                                    const float* sinks, const float* gate, cudaStream_t stream) {
     if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
     if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 ||
         max_q_len <= 0 || num_splits < 1)
@@ -1485,6 +1519,9 @@ RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* bl
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window; p.num_splits = num_splits; p.q_filter = q_filter;
+    p.cap_log2e = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+    p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+    p.sinks = sinks; p.gate = gate;
     const int G = nh / nkv;
     const int m_tile = mode == 1 ? 16 : 64;
     p.row_tiles = (max_q_len * G + m_tile - 1) / m_tile;
@@ -1492,10 +1529,19 @@ RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* bl
     if (st != RV_OK) return st;
     if (num_splits > 1) {
         RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3((n_tokens * nh + COMBINE_ROWS - 1) / COMBINE_ROWS), dim3(128), 0, stream,
-                                 p.part_o, p.part_ml, p.out, n_tokens * nh, num_splits);
+                                 p.part_o, p.part_ml, p.out, n_tokens * nh, num_splits, p.sinks, p.gate, nh);
         return rv_launch_status();
     }
     return RV_OK;
+}
+
+RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* block_tables, const int* cu_seqlens,
+                                 const int* ctx_lens, void* out, float* scratch, int n_tokens, int num_seqs,
+                                 int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
+                                 int mode, int max_q_len, int num_splits, int q_filter, cudaStream_t stream) {
+    return rv_flash_attention_ex(q, cache, block_tables, cu_seqlens, ctx_lens, out, scratch, n_tokens, num_seqs, nh, nkv, hd,
+                                 page_size, max_blocks, scale, window, mode, max_q_len, num_splits, q_filter, 0.f, nullptr,
+                                 nullptr, stream);
 }
 
 // The TMA-fed decode kernel for the sequences of a step that bring one token (q_filter 1) or for
@@ -1503,11 +1549,11 @@ RV_EXPORT int rv_flash_attention(const void* q, const void* cache, const int* bl
 // plus the number of pages of the cache layer (for the tensor map), the status word of bounded
 // waits and `early` (request keys before griddepcontrol.wait).  Refuses (RV_ERR_UNSUPPORTED) head
 // sizes other than 64 and 128 and pages of fewer than 8 keys: the caller falls back to rv_flash_attention.
-RV_EXPORT int rv_flash_decode_tma(const void* q, const void* cache, long long num_pages, const int* block_tables,
-                                  const int* cu_seqlens, const int* ctx_lens, void* out, float* scratch, int n_tokens,
-                                  int num_seqs, int nh, int nkv, int hd, int page_size, int max_blocks, float scale,
-                                  int window, int max_q_len, int num_splits, int q_filter, int* status, int early,
-                                  cudaStream_t stream) {
+RV_EXPORT int rv_flash_decode_tma_ex(const void* q, const void* cache, long long num_pages, const int* block_tables,
+                                     const int* cu_seqlens, const int* ctx_lens, void* out, float* scratch, int n_tokens,
+                                     int num_seqs, int nh, int nkv, int hd, int page_size, int max_blocks, float scale,
+                                     int window, int max_q_len, int num_splits, int q_filter, int* status, int early,
+                                     float softcap, const float* sinks, const float* gate, cudaStream_t stream) {
 #ifdef RV_HAVE_TMA_DECODE
     if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
     if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 ||
@@ -1533,6 +1579,9 @@ RV_EXPORT int rv_flash_decode_tma(const void* q, const void* cache, long long nu
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window; p.num_splits = num_splits; p.q_filter = q_filter;
+    p.cap_log2e = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+    p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+    p.sinks = sinks; p.gate = gate;
     const int G = nh / nkv;
     p.row_tiles = (max_q_len * G + 15) / 16;
     const int smem = 2 * TMA_STAGES * TMA_TILE_BYTES + 1024;
@@ -1544,13 +1593,23 @@ RV_EXPORT int rv_flash_decode_tma(const void* q, const void* cache, long long nu
     if (st != RV_OK) return st;
     if (num_splits > 1) {
         RV_LAUNCH_ST = rv_launch(flash_combine_kernel, dim3((n_tokens * nh + COMBINE_ROWS - 1) / COMBINE_ROWS), dim3(128), 0, stream,
-                                 p.part_o, p.part_ml, p.out, n_tokens * nh, num_splits);
+                                 p.part_o, p.part_ml, p.out, n_tokens * nh, num_splits, p.sinks, p.gate, nh);
         return rv_launch_status();
     }
     return RV_OK;
 #else
     return RV_ERR_UNSUPPORTED;
 #endif
+}
+
+RV_EXPORT int rv_flash_decode_tma(const void* q, const void* cache, long long num_pages, const int* block_tables,
+                                  const int* cu_seqlens, const int* ctx_lens, void* out, float* scratch, int n_tokens,
+                                  int num_seqs, int nh, int nkv, int hd, int page_size, int max_blocks, float scale,
+                                  int window, int max_q_len, int num_splits, int q_filter, int* status, int early,
+                                  cudaStream_t stream) {
+    return rv_flash_decode_tma_ex(q, cache, num_pages, block_tables, cu_seqlens, ctx_lens, out, scratch, n_tokens, num_seqs, nh,
+                                  nkv, hd, page_size, max_blocks, scale, window, max_q_len, num_splits, q_filter, status, early,
+                                  0.f, nullptr, nullptr, stream);
 }
 
 // The evenly cut decode kernel fed by TMA (head sizes 64 and 128, pages of at least 8 keys; else

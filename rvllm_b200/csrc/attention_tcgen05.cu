@@ -82,6 +82,12 @@ struct AttnParams {
     int nh, nkv, page_shift, page_size, max_blocks;
     float scale_log2e;
     int window;
+    // options (rv_attention_tcgen05_ex): a capped score c tanh(s / c), a sink per head in the softmax denominator,
+    // a gate per (token, head) on the output
+    float cap_log2e;               // c log2(e); 0: no cap
+    float scale_over_cap;          // scale / c
+    const float* sinks;            // [nh] or null
+    const float* gate;             // [n_tokens, nh] or null
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
@@ -408,6 +414,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tcgen05_fence_before();
             __syncwarp();
             const int key0 = t * KV_TILE;
+            // With a cap the scores become c log2(e) tanh(scale s / c) here (tanh as 1 - 2 / (e^2x + 1)), before the
+            // masks, and the scale below is 1.
+            const float eff_scale = p.cap_log2e > 0.f ? 1.f : p.scale_log2e;
+            if (p.cap_log2e > 0.f) {
+                const float k2 = p.scale_over_cap * 2.885390081777927f;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float ea = fast_exp2(__uint_as_float(s0[e]) * k2), eb = fast_exp2(__uint_as_float(s1[e]) * k2);
+                    s0[e] = __float_as_uint(p.cap_log2e * (1.f - __fdividef(2.f, ea + 1.f)));
+                    s1[e] = __float_as_uint(p.cap_log2e * (1.f - __fdividef(2.f, eb + 1.f)));
+                }
+            }
             // Scores stay raw in the registers; scale and reference maximum are applied in one FMA
             // before the exponential.  Only tiles that cross the row's visible range need masks.
             if (!(key0 + KV_TILE - 1 <= pos && key0 >= lo)) {
@@ -427,7 +445,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 mx[3] = max3(mx[3], __uint_as_float(s1[e + 2]), __uint_as_float(s1[e + 3]));
             }
             const float m_raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            const float m_tile = m_raw * p.scale_log2e;       // the scale is positive: the maximum commutes
+            const float m_tile = m_raw * eff_scale;           // the scale is positive: the maximum commutes
             // raise the reference maximum only when it is far behind: O then needs a pass
             const bool first_data = m_ref == -INFINITY && m_tile > -INFINITY;
             const bool raise = first_data || m_tile > m_ref + RESCALE_LOG2;
@@ -472,7 +490,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const int e = 2 * j;
                 float a0, a1;
                 fma2(a0, a1, __uint_as_float(e < 32 ? s0[e] : s1[e - 32]), __uint_as_float(e + 1 < 32 ? s0[e + 1] : s1[e + 1 - 32]),
-                     p.scale_log2e, neg_m);
+                     eff_scale, neg_m);
                 const float x0 = fast_exp2(a0), x1 = fast_exp2(a1);
                 add2(l_tile, l_tile2, x0, x1);
                 __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
@@ -494,7 +512,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             ok = mbar_wait(bar_o_full0 + 8 * ((n_it - 1) & 1), ((n_it - 1) >> 1) & 1, &abort_flag, 10);
             tcgen05_fence_after();
             if (ok) {
-                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+                float num = 1.f, den = l_run;
+                if (p.sinks && in_range) {           // exp(sink) joins the denominator; it has no value
+                    const float sk = p.sinks[head] * 1.4426950408889634f;
+                    const float m_new = fmaxf(m_ref, sk);
+                    num = fast_exp2(m_ref - m_new);
+                    den = l_run * num + fast_exp2(sk - m_new);
+                }
+                float inv = den > 0.f ? num / den : 0.f;
+                if (p.gate && in_range) inv *= p.gate[(size_t)(q_start + tok_i) * p.nh + head];
                 __nv_bfloat16* dst = p.out + ((size_t)(q_start + tok_i) * p.nh + head) * HEAD_DIM;
 #pragma unroll
                 for (int c = 0; c < HEAD_DIM; c += 32) {
@@ -563,10 +589,13 @@ RV_EXPORT int rv_attention_tcgen05_head_dim() { return HEAD_DIM; }
 // Attention of the sequences that bring more than one token to the step (the others are left to
 // the decode kernel).  Refuses (RV_ERR_UNSUPPORTED) what it is not built for: a head size other
 // than HEAD_DIM, a group of more than 128 heads, pages of fewer than 8 keys.
-RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long num_pages, const int* block_tables,
-                                   const int* cu_seqlens, const int* ctx_lens, void* out, int n_tokens, int num_seqs,
-                                   int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
-                                   int max_q_len, int* status, cudaStream_t stream) {
+// `softcap` > 0: scaled scores pass softcap * tanh(s / softcap); `sinks` (float [nh]): exp(sink) joins each head's softmax
+// denominator; `gate` (float [n_tokens, nh]): multiplies each head's output.  Null / 0: absent.
+RV_EXPORT int rv_attention_tcgen05_ex(const void* q, const void* cache, long long num_pages, const int* block_tables,
+                                      const int* cu_seqlens, const int* ctx_lens, void* out, int n_tokens, int num_seqs,
+                                      int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
+                                      int max_q_len, int* status, float softcap, const float* sinks, const float* gate,
+                                      cudaStream_t stream) {
     if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
     if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 || max_q_len <= 0)
         return RV_ERR_BAD_SIZE;
@@ -589,6 +618,9 @@ RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long n
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window;
+    p.cap_log2e = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+    p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+    p.sinks = sinks; p.gate = gate;
     const int smem = Q_BYTES + (NK + NV) * KV_BYTES + 256;
     static RvPerDevice configured;
     if (int e = rv_configure_smem(configured, attention_tcgen05_kernel, smem)) return e;
@@ -597,4 +629,12 @@ RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long n
     if (grid.y > 65535 || grid.z > 65535) return RV_ERR_UNSUPPORTED;
     RV_LAUNCH_ST = rv_launch(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), smem, stream, map_q, map_kv, p);
     return rv_launch_status();
+}
+
+RV_EXPORT int rv_attention_tcgen05(const void* q, const void* cache, long long num_pages, const int* block_tables,
+                                   const int* cu_seqlens, const int* ctx_lens, void* out, int n_tokens, int num_seqs,
+                                   int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
+                                   int max_q_len, int* status, cudaStream_t stream) {
+    return rv_attention_tcgen05_ex(q, cache, num_pages, block_tables, cu_seqlens, ctx_lens, out, n_tokens, num_seqs, nh, nkv, hd,
+                                   page_size, max_blocks, scale, window, max_q_len, status, 0.f, nullptr, nullptr, stream);
 }

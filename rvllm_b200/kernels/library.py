@@ -275,36 +275,40 @@ class CudaKernels:
         when the batch alone cannot fill the GPU); everything else goes to the plain kernel."""
         page = cache_layer.shape[3]
         extras = softcap is not None or sinks is not None or gate is not None
-        if extras or q.dtype != torch.bfloat16 or head_dim % 16 or head_dim > 256 or (page & (page - 1)):
+        if q.dtype != torch.bfloat16 or head_dim % 16 or head_dim > 256 or (page & (page - 1)):
             return self.paged_attention_plain(q, cache_layer, meta, num_heads, num_kv_heads, head_dim, scale, window,
                                               softcap, sinks, gate)
+        self._check_attention_extras(q, num_heads, sinks, gate)
+        x = dict(softcap=softcap, sinks=sinks, gate=gate)
         out = torch.empty_like(q)
         group = num_heads // num_kv_heads
+        # (the evenly cut decode kernel knows neither cap, sink nor gate: such layers stay with the split kernels)
+        balanced = not extras and self._balanced_ok(meta, group, num_kv_heads)
         if self.TCGEN05_ATTENTION and meta.max_q_len >= self.TCGEN05_ATTENTION_MIN_TOKENS and head_dim in (64, 128) \
                 and group <= 128 and page >= 8:
-            self.attention_tcgen05(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
+            self.attention_tcgen05(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, **x)
             if meta.num_decode:
-                if self._balanced_ok(meta, group, num_kv_heads):
+                if balanced:
                     self.flash_decode_balanced(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
                 else:
-                    self.decode_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, q_filter=1)
+                    self.decode_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, q_filter=1, **x)
             return out
         if meta.max_q_len == 1:
-            if self._balanced_ok(meta, group, num_kv_heads):
+            if balanced:
                 self.flash_decode_balanced(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window)
             else:
                 self.decode_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                                      num_splits=self.decode_splits(meta, num_heads, num_kv_heads))
+                                      num_splits=self.decode_splits(meta, num_heads, num_kv_heads), **x)
         elif meta.num_decode == 0:
-            self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, mode=0)
+            self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, mode=0, **x)
         else:
             self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                                 mode=0, q_filter=2)
-            self.decode_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, q_filter=1)
+                                 mode=0, q_filter=2, **x)
+            self.decode_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, q_filter=1, **x)
         return out
 
     def decode_attention(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                         num_splits=1, q_filter=0, status=None, tma=None, early=None):
+                         num_splits=1, q_filter=0, status=None, tma=None, early=None, softcap=None, sinks=None, gate=None):
         """Attention of the step's one-token sequences (all of them, or with q_filter 1 those among
         longer ones) with the decode tiling, the keys split over `num_splits` CTAs: the tiles come by
         TMA where the kernel is built for the sizes (head size 64 or 128, pages of 8 keys or more),
@@ -312,7 +316,8 @@ class CudaKernels:
         tma = self.TMA_DECODE if tma is None else tma
         if not tma or head_dim not in (64, 128) or cache_layer.shape[3] < 8:
             return self.flash_attention(q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                                        mode=1, num_splits=num_splits, q_filter=q_filter, max_q_len=1)
+                                        mode=1, num_splits=num_splits, q_filter=q_filter, max_q_len=1,
+                                        softcap=softcap, sinks=sinks, gate=gate)
         _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
         lib = self._lib("attention_flash.cu", (f"-DHEAD_DIM={head_dim}",))
         T = q.shape[0]
@@ -320,12 +325,12 @@ class CudaKernels:
         if num_splits > 1:
             scratch = torch.empty((num_splits * T * num_heads * (head_dim + 2),), dtype=torch.float32, device=q.device)
         early = self.TMA_DECODE_EARLY if early is None else early
-        st = lib.rv_flash_decode_tma(
+        st = lib.rv_flash_decode_tma_ex(
             _ptr(q), _ptr(cache_layer), ctypes.c_longlong(cache_layer.shape[0]), _ptr(meta.block_tables), _ptr(meta.cu_seqlens),
             _ptr(meta.ctx_lens), _ptr(out), _ptr(scratch), c_int(T), c_int(meta.num_seqs), c_int(num_heads), c_int(num_kv_heads),
             c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks), c_float(scale), c_int(window or 0), c_int(1),
             c_int(num_splits), c_int(q_filter), _ptr(status if status is not None else self._status),
-            c_int(1 if (early and self.pdl) else 0), self._stream())
+            c_int(1 if (early and self.pdl) else 0), c_float(softcap or 0.0), _ptr(sinks), _ptr(gate), self._stream())
         _check("flash_decode_tma", st)
         return out
 
@@ -404,31 +409,34 @@ class CudaKernels:
         return out
 
     def flash_attention(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                        mode=0, num_splits=1, q_filter=0, max_q_len=None):
+                        mode=0, num_splits=1, q_filter=0, max_q_len=None, softcap=None, sinks=None, gate=None):
         _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
         lib = self._lib("attention_flash.cu", (f"-DHEAD_DIM={head_dim}",))
         T = q.shape[0]
         scratch = None
         if num_splits > 1:
             scratch = torch.empty((num_splits * T * num_heads * (head_dim + 2),), dtype=torch.float32, device=q.device)
-        st = lib.rv_flash_attention(
+        st = lib.rv_flash_attention_ex(
             _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens),
             _ptr(out), _ptr(scratch), c_int(T), c_int(meta.num_seqs), c_int(num_heads), c_int(num_kv_heads),
             c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks), c_float(scale), c_int(window or 0),
-            c_int(mode), c_int(max_q_len or meta.max_q_len), c_int(num_splits), c_int(q_filter), self._stream())
+            c_int(mode), c_int(max_q_len or meta.max_q_len), c_int(num_splits), c_int(q_filter), c_float(softcap or 0.0),
+            _ptr(sinks), _ptr(gate), self._stream())
         _check("flash_attention", st)
         return out
 
-    def attention_tcgen05(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, status=None):
+    def attention_tcgen05(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, status=None,
+                          softcap=None, sinks=None, gate=None):
         """The tcgen05 flash-attention kernel for the sequences of a step that bring more than one
         token (bfloat16, head size 64 or 128, groups of up to 128 heads, pages of at least 8 keys)."""
         _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
         lib = self._lib("attention_tcgen05.cu", (f"-DHEAD_DIM={head_dim}",))
-        st = lib.rv_attention_tcgen05(
+        st = lib.rv_attention_tcgen05_ex(
             _ptr(q), _ptr(cache_layer), ctypes.c_longlong(cache_layer.shape[0]), _ptr(meta.block_tables),
             _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(out), c_int(q.shape[0]), c_int(meta.num_seqs),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cache_layer.shape[3]), c_int(meta.max_blocks),
-            c_float(scale), c_int(window or 0), c_int(meta.max_q_len), _ptr(status if status is not None else self._status), self._stream())
+            c_float(scale), c_int(window or 0), c_int(meta.max_q_len), _ptr(status if status is not None else self._status),
+            c_float(softcap or 0.0), _ptr(sinks), _ptr(gate), self._stream())
         _check("attention_tcgen05", st)
         return out
 
