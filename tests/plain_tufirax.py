@@ -1,7 +1,8 @@
 """Plain, slow implementation of the Tufirax decoder, used as the oracle of its tests.
 
 Whole sequences only: no cache, no state carried between calls, no batching; one function per
-mechanism, torch used purely as an array library (float64 on the CPU).  It shares no code with
+mechanism (`store`, where a function has it, is applied to what an engine keeps between two kernels in
+the activations' type - the identity, or a rounding to bfloat16 that measures what that storage costs), torch used purely as an array library (float64 on the CPU).  It shares no code with
 the engine under ``rvllm_b200``: the configuration is a plain dictionary and the weights a plain
 dictionary name -> tensor.
 
@@ -30,6 +31,15 @@ from typing import Dict, List, Sequence
 import torch
 
 F64 = torch.float64
+
+
+def _keep(t: torch.Tensor) -> torch.Tensor:
+    return t
+
+
+def round_to_bfloat16(t: torch.Tensor) -> torch.Tensor:
+    """What storing a tensor in bfloat16 between two kernels does to it (the arithmetic stays float64)."""
+    return t.to(torch.bfloat16).to(t.dtype)
 
 
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
@@ -75,20 +85,21 @@ def sink_softmax_attention(q, k, v, scale: float, softcap: float, sink: torch.Te
     return out
 
 
-def attention_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float, start: int = 0) -> torch.Tensor:
+def attention_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float, start: int = 0,
+                    store=_keep) -> torch.Tensor:
     T = h.shape[0]
     H, G, d = m["heads"], m["kv_heads"], m["dim"]
     q = h @ w[p + "q"].t()
     k = h @ w[p + "k"].t()
-    v = k.view(T, G, d)
+    v = store(k.view(T, G, d))
     qn = (rms(q, eps) * w[p + "q.norm"]).view(T, H, d)
     kn = (rms(k, eps) * w[p + "k.norm"]).view(T, G, d)
     pos = range(start, start + T)
     qn = rotate_leading(qn, pos, m["rot"]["dims"], m["rot"]["base"])
     kn = rotate_leading(kn, pos, m["rot"]["dims"], m["rot"]["base"])
-    o = sink_softmax_attention(qn, kn, v, m["scale"], m["softcap"], w[p + "sink"])
+    o = sink_softmax_attention(store(qn), store(kn), v, m["scale"], m["softcap"], w[p + "sink"])
     gate = torch.sigmoid(h @ w[p + "g"].t())                       # [T, H]
-    o = o * gate[:, :, None]
+    o = store(o * gate[:, :, None])
     return o.reshape(T, -1) @ w[p + "o"].t()
 
 
@@ -123,28 +134,31 @@ def grouped_rms(y: torch.Tensor, parts: int, eps: float) -> torch.Tensor:
     return rms(y.view(T, parts, W // parts), eps).reshape(T, W)
 
 
-def mamba2_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
+def mamba2_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float, store=_keep) -> torch.Tensor:
     T = h.shape[0]
     heads, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
     inner = heads * P
     proj = h @ w[p + "in"].t()
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
-    xbc = silu(causal_conv(xbc, w[p + "conv"], w[p + "conv.b"]))
+    xbc = store(silu(causal_conv(xbc, w[p + "conv"], w[p + "conv.b"])))
     x = xbc[:, :inner].reshape(T, heads, P)
     B = xbc[:, inner:inner + G * N].reshape(T, G, N)
     C = xbc[:, inner + G * N:].reshape(T, G, N)
     dt = softplus(dt + w[p + "dt_bias"][None, :])
     y = selective_scan(x, B, C, dt, w[p + "A_log"], w[p + "D"], G).reshape(T, inner)
-    y = grouped_rms(y * silu(z), m["norm_groups"], eps) * w[p + "norm"]
+    y = store(grouped_rms(y * silu(z), m["norm_groups"], eps) * w[p + "norm"])
     return y @ w[p + "o"].t()
 
 
-def dense_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
-    return (gelu_tanh(h @ w[p + "gate"].t()) * (h @ w[p + "up"].t())) @ w[p + "down"].t()
+def dense_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, store=_keep) -> torch.Tensor:
+    return store(gelu_tanh(h @ w[p + "gate"].t()) * (h @ w[p + "up"].t())) @ w[p + "down"].t()
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], residuals: List[torch.Tensor] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence.  `residuals`, if a list, receives x after every layer run."""
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], residuals: List[torch.Tensor] = None,
+            store=_keep) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence.  `residuals`, if a list, receives x after every layer run.
+    The stream x itself is never passed through `store` (it is float32 in every engine type); the copy of it
+    that a sublayer's products read is."""
     w = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in w.items()}
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.tensor(list(tokens), dtype=torch.long)]
@@ -152,17 +166,17 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], residu
         src = layer.get("weights_of", i)
         p = f"l{src}."
         if layer["type"] == "attention":
-            y = attention_mixer(x, w, p + "mix.", layer["mixer"], eps)
+            y = attention_mixer(store(x), w, p + "mix.", layer["mixer"], eps, store=store)
         elif layer["type"] == "mamba2":
-            y = mamba2_mixer(x, w, p + "mix.", layer["mixer"], eps)
+            y = mamba2_mixer(store(x), w, p + "mix.", layer["mixer"], eps, store=store)
         else:
             raise ValueError(f"unknown layer type {layer['type']!r}")
         x = x + rms(y, eps) * w[p + "norm1"]
         if layer.get("mlp") is not None:
-            x = x + rms(dense_ff(x, w, p + "mlp."), eps) * w[p + "norm2"]
+            x = x + rms(dense_ff(store(x), w, p + "mlp.", store=store), eps) * w[p + "norm2"]
         if residuals is not None:
             residuals.append(x.clone())
-    return (rms(x, eps) * w["final.norm"]) @ w["head"].t()
+    return store(rms(x, eps) * w["final.norm"]) @ w["head"].t()
 
 
 def greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], n_new: int) -> List[int]:

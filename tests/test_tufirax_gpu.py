@@ -106,7 +106,7 @@ def _attention_case(nh, nkv, hd, ctxs, q_lens, page, dtype, seed, far=None, sink
     vs = [v.to(dtype).double() for v in vs]
     sinks = rnd(nh, seed=seed + 5, scale=1.5).float()
     if sink_value is not None:
-        sinks[0] = sink_value
+        sinks[1] = sink_value          # (head 1: not one of the heads the far key is aligned with)
     T = sum(q_lens)
     gate = torch.rand(T, nh, generator=torch.Generator().manual_seed(seed + 6)).float()
     cache, meta = paged_setup([k.float() for k in ks], [v.float() for v in vs], q_lens, page, dtype, seed=seed)
@@ -141,9 +141,9 @@ def test_tensor_core_attention_paths_with_cap_sink_gate(K, hd, page):
     x = dict(softcap=cap, sinks=sinks, gate=gate)
     ref = K.paged_attention_plain(q, cache, meta, nh, nkv, hd, scale, None, cap, sinks, gate)
     assert rel_err(ref, want) < 6e-3
-    assert float(want.view(-1, nh, hd)[:, 0].abs().max()) < 0.02 * float(want.abs().max())      # head 0: the sink has the weight
+    assert float(want.view(-1, nh, hd)[:, 1].abs().max()) < 0.02 * float(want.abs().max())      # head 1: the sink has the weight
     far_row = sum(q_lens[:2])                                                                   # the decoded token of sequence 2
-    assert float(want.view(-1, nh, hd)[far_row, 4].mean()) > 2.0                                 # the far key's value shows
+    assert float(want.view(-1, nh, hd)[far_row, 4].mean() / gate[far_row, 4].cpu()) > 2.5        # the far key (value 5) has most of the weight
     out = K.paged_attention(q, cache, meta, nh, nkv, hd, scale, None, **x)                      # the dispatch a model takes
     assert rel_err(out, want) < 8e-3
     for name, run in {
@@ -171,7 +171,7 @@ def test_decode_only_step_with_splits(K):
     out = K.paged_attention(q, cache, meta, nh, nkv, hd, scale, None, softcap=cap, sinks=sinks, gate=gate)
     assert K.decode_splits(meta, nh, nkv) > 1
     assert rel_err(out, want) < 8e-3
-    assert float(want.view(-1, nh, hd)[0, 0].mean()) > 2.0
+    assert float(want.view(-1, nh, hd)[0, 0].mean() / gate[0, 0].cpu()) > 2.5
     K.raise_on_abort()
 
 
@@ -267,7 +267,6 @@ def test_gated_group_norm(K, dtype, width, parts):
 LENGTHS = {"a": (45, 170, 33, 81, 1, 138), "b": (90, 37, 310, 64, 151, 2)}
 SCHEDULES = {"whole": TT.schedule_whole, "bulk_tail": TT.schedule_bulk_tail, "portions": TT.schedule_portions,
              "mixed": TT.schedule_mixed}
-REPLAY_TOL = {"float32": 1e-4, "bfloat16": 3e-2}
 _cache = {}
 
 
@@ -277,8 +276,8 @@ def _reference(which):
         folder = X.write_folder({"a": X.small_a, "b": X.small_b}[which](), seed=5, edit=X.lively)
         vocab = load_config(folder).vocab_size
         reqs = random_requests(vocab, LENGTHS[which], seed=4)
-        _cache[which] = (folder, vocab, reqs, X.plain_logits(folder, reqs))
-    return _cache[which]
+        _cache[which] = (folder, vocab, reqs, X.plain_logits(folder, reqs), X.plain_logits(folder, reqs, rounded=True))
+    return _cache[which][:4]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -297,7 +296,14 @@ def test_replay_matches_plain(tmp_path, which, schedule, dtype):
         engine.cache.check()
         assert not engine.cache.requests
     got = TT.read_logits(str(tmp_path), trace, vocab)
-    TT.compare(got, ref, REPLAY_TOL[dtype], f"{which}/{schedule}/{dtype}")
+    what = f"{which}/{schedule}/{dtype}"
+    if dtype == "float32":
+        TT.compare(got, ref, 1e-4, what)
+    else:
+        # against what storing activations in bfloat16 costs by itself on the same requests (no position beyond
+        # 1.5 x its worst, the median within 1.25 x its median), and no position beyond a plain bound either
+        TT.compare_bfloat16(got, ref, _cache[which][4], what)
+        TT.compare(got, ref, 8e-2, what)
 
 
 def test_generation_through_the_entry_point():

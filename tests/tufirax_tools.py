@@ -103,6 +103,9 @@ def read_folder(folder: str):
     return cfg, load_file(os.path.join(folder, "model.safetensors"))
 
 
-def plain_logits(folder: str, requests: Dict[str, List[int]]) -> Dict[str, torch.Tensor]:
+def plain_logits(folder: str, requests: Dict[str, List[int]], rounded: bool = False) -> Dict[str, torch.Tensor]:
+    """float64 logits of the plain implementation; `rounded`: with everything an engine stores between two kernels
+    rounded to bfloat16, which measures what that storage costs by itself on these requests."""
     cfg, w = read_folder(folder)
-    return {rid: P.forward(cfg, w, toks) for rid, toks in requests.items()}
+    store = P.round_to_bfloat16 if rounded else P._keep
+    return {rid: P.forward(cfg, w, toks, store=store) for rid, toks in requests.items()}
