@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200: decode tokens per second, prefill, roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape NAME]
-                    [--workload decode|serve] [--impl ours|reference]
+                    [--workload decode|serve|tufirax] [--impl ours|reference]
 
 The default run has the layer sizes of Llama-3.1-8B (32 layers, hidden 4096, 32 query heads,
 8 key/value heads of 128, MLP 14336, vocabulary 128256, llama3 rotary scaling) with random
@@ -362,6 +362,196 @@ def serve_workload(shape_name, layers, requests, output_len, budget, eager):
         "clocks": ck}
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --workload tufirax: the Tufirax design (attention with whole-row q/k norms, capped scores, a sink and a head gate;
+# mamba2 mixers; GELU-gated feed-forwards; norms on the sublayers' outputs around a float32 stream) at layer sizes
+# that resemble real models, beside the Llama decoder of this engine at the same width, heads, feed-forward and
+# depth; then each of the design's own kernels alone beside the like kernel of the Llama path, with the bytes it has
+# to move over its time against the measured copy bandwidth.  Random weights; its own JSON line.
+TUFIRAX_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, rot=64, ff=8192, m_heads=64, m_vdim=64, state=128, groups=8, layers=8),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, rot=128, ff=14336, m_heads=128, m_vdim=64, state=128, groups=8, layers=8),
+}
+
+
+def tufirax_pair(size: dict, vocab: int = 32768):
+    """(Tufirax configuration, Llama configuration) of equal width, heads, feed-forward and depth.  The Tufirax layers
+    alternate attention and mamba2, each with a feed-forward."""
+    att = {"type": "attention", "mixer": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"],
+                                          "scale": size["dim"] ** -0.5, "softcap": 30.0, "rot": {"dims": size["rot"], "base": 500000.0}},
+           "mlp": {"kind": "dense", "ff": size["ff"]}}
+    mam = {"type": "mamba2", "mixer": {"heads": size["m_heads"], "vdim": size["m_vdim"], "state": size["state"], "groups": size["groups"],
+                                       "conv": 4, "norm_groups": size["groups"]}, "mlp": {"kind": "dense", "ff": size["ff"]}}
+    tfx = {"architecture": "Tufirax", "width": size["width"], "vocab": vocab, "norm": {"eps": 1e-6},
+           "layers": [att if i % 2 == 0 else mam for i in range(size["layers"])]}
+    llama = {"architectures": ["LlamaForCausalLM"], "hidden_size": size["width"], "num_hidden_layers": size["layers"],
+             "num_attention_heads": size["heads"], "num_key_value_heads": size["kv_heads"], "head_dim": size["dim"],
+             "intermediate_size": size["ff"], "vocab_size": vocab, "max_position_embeddings": 8192, "rms_norm_eps": 1e-6,
+             "rope_theta": 500000.0, "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "bfloat16"}
+    return tfx, llama
+
+
+def _time_kernel(fn, iters=5, flush=None):
+    """Milliseconds of one call of fn, the best of `iters`, each after a write of a buffer larger than L2."""
+    import torch
+    best = float("inf")
+    fn()
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b))
+    return best
+
+
+def run_tufirax(args):
+    import torch
+
+    from rvllm_b200 import LLM, config_from_dict
+    from rvllm_b200.engine import StepEntry
+    from rvllm_b200.kernels import AttentionMeta
+
+    peaks = measured_peaks()
+    PROMPT, CTX, batch = 2048, 4096, args.batch
+    gen = torch.Generator().manual_seed(0)
+    out = {"workload": "tufirax", "dtype": "bf16", "data": "synthetic", "peaks": peaks["source"], "prompt_len": PROMPT, "batch": batch,
+           "steps": args.steps, "warmup": args.warmup, "models": {}, "kernels": {}}
+
+    def measure(cfg_dict):
+        config = config_from_dict(cfg_dict)
+        llm = LLM(config=config, random_weights=True, seed=0, dtype="bfloat16", block_size=16, num_blocks=batch * (CTX // 16) + 8,
+                  max_model_len=CTX, max_num_seqs=batch, max_num_batched_tokens=PROMPT, enforce_eager=args.eager)
+        runner, V = llm.engine.runner, llm.engine.spec.vocab_size
+        p = torch.randint(0, V, (PROMPT,), generator=gen).tolist()
+        for _ in range(3):
+            runner.step([StepEntry("w", p, [PROMPT - 1])])
+            runner.finish("w")
+        torch.cuda.synchronize()
+        pf = []
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            runner.step([StepEntry("p", p, [PROMPT - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            runner.finish("p")
+            pf.append(a.elapsed_time(b))
+        ids = [f"d{i}" for i in range(batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, torch.randint(0, V, (PROMPT,), generator=gen).tolist(), [])])
+        for _ in range(args.warmup):
+            runner.step([StepEntry(r, [1], [0]) for r in ids])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            runner.step([StepEntry(r, [1], [0]) for r in ids])
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        for rid in ids:
+            runner.finish(rid)
+        kernels = llm.engine.kernels
+        del llm
+        torch.cuda.empty_cache()
+        return {"prefill_ms": round(min(pf), 3), "prefill_tok_s": round(PROMPT / (min(pf) / 1e3), 1),
+                "decode_ms_per_step": round(ms, 4), "decode_tok_s": round(batch / (ms / 1e3), 1)}, kernels
+
+    K = None
+    for name in (args.sizes.split(",") if args.sizes else list(TUFIRAX_SIZES)):
+        tfx, llama = tufirax_pair(TUFIRAX_SIZES[name])
+        a, K = measure(tfx)
+        b, K = measure(llama)
+        out["models"][name] = {"tufirax": a, "llama_same_size": b, "layers": TUFIRAX_SIZES[name]["layers"],
+                               "prefill_ratio": round(a["prefill_tok_s"] / b["prefill_tok_s"], 3),
+                               "decode_ratio": round(a["decode_tok_s"] / b["decode_tok_s"], 3)}
+
+    # ---- the design's kernels alone, at the "4k" sizes, beside the like kernel of the Llama path ------------------
+    z = TUFIRAX_SIZES["4k"]
+    dev, bf = "cuda", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bw = peaks["hbm_gbs"] * 1e9
+
+    def row(name, ms, nbytes, like=None):
+        out["kernels"][name] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / (ms / 1e3) / bw, 3)}
+        if like is not None:
+            out["kernels"][name]["like"] = like
+
+    T, W, FF = PROMPT, z["width"], z["ff"]
+    y = torch.randn(T, W, device=dev)
+    g = torch.ones(W, dtype=bf, device=dev)
+    res = torch.randn(T, W, device=dev)
+    xb = torch.randn(T, W, device=dev).to(bf)
+    ms_like = _time_kernel(lambda: K.rmsnorm(xb, g, 1e-6), flush=flush)
+    like = {"kernel": "rmsnorm", "ms": round(ms_like, 4), "frac_hbm": round(T * W * 4 / (ms_like / 1e3) / bw, 3)}
+    row("residual_rmsnorm", _time_kernel(lambda: K.residual_rmsnorm(y, g, 1e-6, res, bf), flush=flush), T * W * (4 + 4 + 4 + 2), like)
+    gu = torch.randn(T, 2 * FF, device=dev)
+    gub = gu.to(bf)
+    ms_like = _time_kernel(lambda: K.silu_mul(gub), flush=flush)
+    like = {"kernel": "silu_mul", "ms": round(ms_like, 4), "frac_hbm": round(T * FF * 6 / (ms_like / 1e3) / bw, 3)}
+    row("act_mul_gelu", _time_kernel(lambda: K.act_mul(gu, "gelu_tanh", bf), flush=flush), T * FF * (8 + 2), like)
+
+    # attention: one prompt of 2,048 tokens, and a decode step of `batch` sequences behind 2,048 tokens
+    nh, nkv, hd = z["heads"], z["kv_heads"], z["dim"]
+    sinks = torch.zeros(nh, device=dev)
+
+    def attention_case(q_len, ctx, seqs):
+        pages = seqs * (ctx // 16)
+        cache = torch.randn(pages, 2, nkv, 16, hd, device=dev).to(bf)
+        tables = torch.arange(pages, dtype=torch.int32, device=dev).view(seqs, ctx // 16)
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        meta = AttentionMeta(tables, cu, torch.full((seqs,), ctx, dtype=torch.int32, device=dev),
+                             torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len), None, seqs, q_len, ctx, 16,
+                             seqs if q_len == 1 else 0)
+        q = torch.randn(seqs * q_len, nh * hd, device=dev).to(bf)
+        gate = torch.rand(seqs * q_len, nh, device=dev)
+        return q, cache, meta, gate
+
+    q, cache, meta, gate = attention_case(PROMPT, PROMPT, 1)
+    flops = 4.0 * nh * hd * PROMPT * PROMPT / 2
+    ms_like = _time_kernel(lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None), flush=flush)
+    ms = _time_kernel(lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None, softcap=30.0, sinks=sinks, gate=gate), flush=flush)
+    out["kernels"]["attention_prefill_cap_sink_gate"] = {
+        "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "frac_bf16": round(flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 3),
+        "like": {"kernel": "attention_prefill", "ms": round(ms_like, 4), "frac_bf16": round(flops / (ms_like / 1e3) / (peaks["bf16_tflops"] * 1e12), 3)}}
+    q, cache, meta, gate = attention_case(1, PROMPT, batch)
+    nbytes = batch * PROMPT * 2 * nkv * hd * 2
+    ms_like = _time_kernel(lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None), flush=flush)
+    like = {"kernel": "attention_decode", "ms": round(ms_like, 4), "frac_hbm": round(nbytes / (ms_like / 1e3) / bw, 3)}
+    row("attention_decode_cap_sink_gate",
+        _time_kernel(lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None, softcap=30.0, sinks=sinks, gate=gate), flush=flush),
+        nbytes, like)
+
+    # the state-space mixer's kernels: a 2,048-token prompt, and a decode step of `batch` sequences
+    H, P, N, G = z["m_heads"], z["m_vdim"], z["state"], z["groups"]
+    inner, ch = H * P, H * P + 2 * G * N
+    wide = 2 * inner + 2 * G * N + H
+    conv_w, conv_b = torch.randn(ch, 4, device=dev).to(bf), torch.zeros(ch, dtype=bf, device=dev)
+    dt_bias, a_log, d_skip = torch.zeros(H, device=dev), torch.zeros(H, device=dev), torch.ones(H, device=dev)
+    norm_w = torch.ones(inner, dtype=bf, device=dev)
+    for label, q_len, seqs in (("prefill", PROMPT, 1), ("decode", 1, batch)):
+        rows = q_len * seqs
+        proj = torch.randn(rows, wide, device=dev)
+        state = torch.zeros(seqs, H * N * P + 3 * ch, device=dev)
+        seq_of = torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len)
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        xbc = K.causal_conv_silu(proj, inner, ch, conv_w, conv_b, seq_of, cu, slots, state, H * N * P, bf)
+        row(f"causal_conv_silu_{label}", _time_kernel(lambda: K.causal_conv_silu(proj, inner, ch, conv_w, conv_b, seq_of, cu, slots, state,
+                                                                                 H * N * P, bf), flush=flush), rows * ch * (4 + 2))
+        yv = K.ssm_scan(xbc, proj, inner + ch, dt_bias, a_log, d_skip, cu, slots, state, H, P, N, G)
+        ms = _time_kernel(lambda: K.ssm_scan(xbc, proj, inner + ch, dt_bias, a_log, d_skip, cu, slots, state, H, P, N, G), flush=flush)
+        row(f"ssm_scan_{label}", ms, rows * (ch * 2 + inner * 4) + seqs * H * N * P * 8)
+        out["kernels"][f"ssm_scan_{label}"]["gflops"] = round(rows * H * P * N * 5 / ms / 1e6, 1)
+        row(f"gated_group_rmsnorm_{label}", _time_kernel(lambda: K.gated_group_rmsnorm(yv, proj, norm_w, 1e-6, G, bf), flush=flush),
+            rows * inner * (4 + 4 + 2))
+    print(json.dumps(out))
+
+
 def run_serve(args):
     print(json.dumps(serve_workload(args.shape, args.layers, args.requests, args.output_len, args.budget, args.eager)))
 
@@ -374,8 +564,10 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES), help="layer sizes of the model")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve"],
-                    help="decode: the contract's line; serve: continuous batching of uneven prompts")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "tufirax"],
+                    help="decode: the contract's line; serve: continuous batching of uneven prompts; tufirax: the Tufirax "
+                         "design at real layer sizes beside the Llama decoder of equal size, and its kernels alone")
+    ap.add_argument("--sizes", default="", help="tufirax: which sizes to run, with commas (default: all)")
     ap.add_argument("--requests", type=int, default=64, help="serve: number of requests")
     ap.add_argument("--output-len", type=int, default=256, help="serve: tokens generated per request")
     ap.add_argument("--budget", type=int, default=2048, help="serve: tokens per step")
@@ -393,7 +585,9 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     ensure_built()
-    if args.workload == "serve":
+    if args.workload == "tufirax":
+        run_tufirax(args)
+    elif args.workload == "serve":
         run_serve(args)
     else:
         run_ours(args)

@@ -89,6 +89,18 @@ class CacheManager:
         el = torch.empty((), dtype=dtype).element_size()
         return sum(2 * n.num_kv_heads * page_size * n.head_dim * el for n in needs.values() if isinstance(n, KvCacheNeed))
 
+    @staticmethod
+    def state_bytes_per_request(needs: Dict[int, object]) -> int:
+        """Bytes of fixed-size state that one request slot holds over all cache slots."""
+        total = 0
+        for n in needs.values():
+            if isinstance(n, StateNeed):
+                count = 1
+                for d in n.shape:
+                    count *= d
+                total += count * torch.empty((), dtype=getattr(torch, n.dtype)).element_size()
+        return total
+
     def view(self, cache_slot: int) -> CacheView:
         gi = self._slot_group.get(cache_slot)
         kv = None

@@ -163,7 +163,9 @@ def cmd_info(args) -> int:
     import torch
     per_token = CacheManager.bytes_per_page(model.cache_needs(), 1, torch.bfloat16)
     print(json.dumps({"architecture": cfg.to_spec().architecture, "parameters": params,
-                      "kv_bytes_per_token_bf16": per_token, "config": cfg.to_dict()}, indent=2))
+                      "kv_bytes_per_token_bf16": per_token,
+                      "state_bytes_per_request": CacheManager.state_bytes_per_request(model.cache_needs()),
+                      "config": cfg.to_dict()}, indent=2))
     return 0
 
 

@@ -144,7 +144,7 @@ class TufiraxConfig:
                 p.append(at + f"`weights_of` must name another layer, got {src!r}")
                 src = None
             layers.append(TufiraxLayer(kind if kind in ("attention", "mamba2") else "attention", mixer, ff, src))
-        # a layer that borrows tensors equals its source in everything but the cache
+        # a layer that borrows tensors runs as its source describes itself (its own description repeats the source's)
         for i, layer in enumerate(layers):
             seen = {i}
             j = layer.weights_of
@@ -153,11 +153,9 @@ class TufiraxConfig:
                     p.append(f"layers[{i}]: `weights_of` runs in a circle")
                     break
                 seen.add(j)
-                src = layers[j]
-                if (src.type, src.mixer, src.ff) != (layer.type, layer.mixer, layer.ff):
-                    p.append(f"layers[{i}] uses the tensors of layer {j} but describes a different layer")
-                    break
-                j = src.weights_of
+                j = layers[j].weights_of
+            else:
+                continue
         max_pos = obj.get("max_positions", DEFAULT_MAX_POSITIONS)
         if not _is_int(max_pos) or max_pos < 1:
             p.append(f"`max_positions` must be a positive integer, got {max_pos!r}")

@@ -70,6 +70,7 @@ static_assert(BN == 256 || BN == 128, "tiles of 256 or 128 columns");
 #define EPI_PLAIN 0
 #define EPI_RESIDUAL 1
 #define EPI_GATED 2
+#define EPI_GATED_GELU 4    // (launcher only) EPI_GATED with the tanh form of GELU in place of SiLU
 #define EPI_ROPE 3          // the q/k/v product: bias, rotation of q and k, k and v into the paged cache
 
 struct GemmParams {
@@ -94,10 +95,15 @@ struct GemmParams {
     const float* cos_t;              // [table_rows, hd / 2] or nullptr (no rotation)
     const float* sin_t;
     int nh, nkv, hd, page_size, table_rows;
+    int act;                       // EPI_GATED: 0 SiLU, 1 the tanh form of GELU
 };
 
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+// the gate's activation: SiLU g sigmoid(g), or (act 1) the tanh form of GELU, which is g sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3))
+__device__ __forceinline__ float gate_act(float g, int act) {
+    return act == 1 ? g / (1.0f + expf(-1.5957691216057308f * (g + 0.044715f * g * g * g))) : silu_f(g);
+}
 // a cluster of CTAs that share a tile's K (the build on single CTAs)
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }     // the four epilogue warps
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
@@ -470,8 +476,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     const int e = v * 8 + 2 * j;
-                                    oh[j] = __floats2bfloat162_rn(silu_f(__uint_as_float(g[e])) * __uint_as_float(u[e]),
-                                                                  silu_f(__uint_as_float(g[e + 1])) * __uint_as_float(u[e + 1]));
+                                    oh[j] = __floats2bfloat162_rn(gate_act(__uint_as_float(g[e]), p.act) * __uint_as_float(u[e]),
+                                                                  gate_act(__uint_as_float(g[e + 1]), p.act) * __uint_as_float(u[e + 1]));
                                 }
                                 *reinterpret_cast<uint4*>(dst + v * 8) = o;
                             }
@@ -479,7 +485,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                             for (int e = 0; e < 32; ++e) {
                                 if (n + e >= half_n) continue;
-                                const float val = silu_f(__uint_as_float(g[e])) * __uint_as_float(u[e]);
+                                const float val = gate_act(__uint_as_float(g[e]), p.act) * __uint_as_float(u[e]);
                                 if (p.out_f32) ((float*)p.out)[(size_t)m * half_n + n + e] = val;
                                 else ((__nv_bfloat16*)p.out)[(size_t)m * half_n + n + e] = __float2bfloat16_rn(val);
                             }
@@ -604,7 +610,7 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const
 // 1 if this library was built for pairs of CTAs
 RV_EXPORT int rv_gemm_tcgen05_is_pair() { return RV_PAIR; }
 
-// epilogue: 0 plain, 1 + residual (bf16 [M, N]), 2 gated (W rows [gate | up], out has N/2 columns).
+// epilogue: 0 plain, 1 + residual (bf16 [M, N]), 2 gated (W rows [gate | up], out has N/2 columns), 4 gated with GELU (tanh form).
 // status: optional device int that receives a non-zero code if a wait inside the kernel gave up.
 // splits (both entry points): 1, or 2 / 4 on the build for single CTAs: the CTAs of a tile share its K as a cluster
 // (see GemmParams); not with the gated epilogue, and with the rotary one only while a CTA's columns hold whole heads.
@@ -620,6 +626,8 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
                                    int M, int N, int K, int epilogue, int* status, int max_ctas, int splits,
                                    cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0) return RV_ERR_BAD_SIZE;
+    const int act = epilogue == EPI_GATED_GELU ? 1 : 0;            // the gated epilogue with the other activation
+    if (act) epilogue = EPI_GATED;
     if (int e = check_splits(splits, K, epilogue, 0)) return e;
     if (K % 8) return RV_ERR_UNSUPPORTED;                          // rows must start on 16-byte boundaries
     if (epilogue == EPI_GATED && (N & 1)) return RV_ERR_BAD_SIZE;
@@ -636,7 +644,7 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
     GemmParams p = {};
     p.out = out; p.residual = epilogue == EPI_RESIDUAL ? (const __nv_bfloat16*)residual : nullptr;
     p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
-    p.splits = splits;
+    p.splits = splits; p.act = act;
     p.m_tiles = (M + TILE_ROWS - 1) / TILE_ROWS;
     // gated: a tile is 128 gate rows and the 128 up rows of the same output columns; gate rows past
     // N/2 read up rows, whose products the epilogue never stores

@@ -58,7 +58,7 @@ struct DecodeGemmParams {
     int* counters;           // [tiles], zero between launches
     int* status;
     int M, N, K;
-    int out_f32, gated;
+    int out_f32, gated;            // gated: 0 no, 1 SiLU-gated, 2 gated with the tanh form of GELU
     int splits, n_tiles;
     int cluster;             // 1: the CTAs of a tile are a thread-block cluster and add their partials in the
                              // cluster's shared memory (M <= 64, 2 <= splits <= 8); scratch and counters unused
@@ -130,8 +130,10 @@ __device__ __forceinline__ float4 load_part(const float* src) {
 
 // SiLU(g) * u.  For a bfloat16 result the hardware's approximations of 2^x and 1/x (two units in the last
 // place of a float, a 4000th of the result's own rounding step) save half of the epilogue's instructions.
-__device__ __forceinline__ float silu_gate(float g, float u, bool exact) {
-    return exact ? g / (1.0f + expf(-g)) * u : __fdividef(g, 1.0f + __expf(-g)) * u;
+// `gelu`: the tanh form of GELU in place of SiLU, as g sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3)).
+__device__ __forceinline__ float silu_gate(float g, float u, bool exact, bool gelu = false) {
+    const float a = gelu ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+    return exact ? g / (1.0f + expf(-a)) * u : __fdividef(g, 1.0f + __expf(-a)) * u;
 }
 
 template <int MB, bool IN_SMEM>
@@ -659,7 +661,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         const float u[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
                         float v[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] = silu_gate(g[j], u[j], p.out_f32 != 0);
+                        for (int j = 0; j < 8; ++j) v[j] = silu_gate(g[j], u[j], p.out_f32 != 0, p.gated == 2);
                         if (p.out_f32) {
                             float* o = (float*)p.out + (size_t)m0 * half_n + n;
 #pragma unroll

@@ -571,7 +571,7 @@ class CudaKernels:
         return self._lib("gemm_tcgen05.cu", defines)
 
     def linear_tcgen05(self, x, weight, residual=None, out_dtype=None, gated=False, status=None, max_ctas=0, pair=None,
-                       splits=None):
+                       splits=None, activation="silu"):
         """The tcgen05 / TMEM / TMA GEMM for bfloat16 (any M; K a multiple of 8).  gated: weight rows
         are [gate | up] and the result is silu(x gate^T) * (x up^T).  `status`: optional int32 device
         tensor that receives a non-zero code if a bounded wait inside the kernel gave up.  `pair`:
@@ -583,7 +583,7 @@ class CudaKernels:
         out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
         if residual is not None:
             _need(residual, "residual", torch.bfloat16, 2)
-        epilogue = 2 if gated else (1 if residual is not None else 0)
+        epilogue = (4 if activation == "gelu_tanh" else 2) if gated else (1 if residual is not None else 0)
         if splits is None:
             splits = self._prefill_splits(M, N, K, gated) if (max_ctas == 0 and pair is None) else 1
         if splits > 1:
@@ -655,7 +655,7 @@ class CudaKernels:
         return splits, bool(cluster)
 
     def linear_decode(self, x, weight, bias=None, residual=None, out_dtype=None, gated=False, splits=None, status=None,
-                      norm=None, cluster=None):
+                      norm=None, cluster=None, activation="silu"):
         """The weight-streaming tcgen05 GEMM for few rows of bfloat16 activations (beyond 128 rows:
         in blocks of 128, K split inside a cluster or not at all).
         norm = (gamma, eps): RMSNorm applied to x inside the kernel (at most 16 rows)."""
@@ -684,7 +684,7 @@ class CudaKernels:
         st = lib.rv_gemm_tcgen05_decode_bf16(
             _ptr(x), _ptr(weight), _ptr(bias), c_int(self._dt(bias, "bias") if bias is not None else 0), _ptr(residual),
             _ptr(out), c_int(1 if out_dtype == torch.float32 else 0), c_int(M), c_int(N), c_int(K),
-            c_int(1 if gated else 0), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch),
+            c_int((2 if activation == "gelu_tanh" else 1) if gated else 0), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch),
             _ptr(self._decode_counters if splits > 1 else None),
             _ptr(status if status is not None else self._status), *self._norm_args(norm, K), self._stream())
         _check("gemm_tcgen05_decode", st)
@@ -795,21 +795,31 @@ class CudaKernels:
         return q
 
     def gate_up_silu(self, x, weight, norm=None) -> torch.Tensor:
-        """silu(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu]: one fused kernel for few bfloat16
-        rows, else the product followed by the SiLU kernel.  norm = (gamma, eps): x is normalised
-        first (RMSNorm), inside the kernel for few rows."""
+        """silu(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu]; see `gate_up_act`."""
+        return self.gate_up_act(x, weight, "silu", norm=norm)
+
+    def gate_up_act(self, x, weight, activation: str = "silu", norm=None) -> torch.Tensor:
+        """act(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu], act = "silu" or "gelu_tanh": one fused kernel for
+        bfloat16 rows (the weight-streaming GEMM for few, the prefill GEMM for many; the activation is applied to the
+        float accumulators in the epilogue), else the product followed by the activation kernel.  norm = (gamma, eps):
+        x is normalised first (RMSNorm), inside the kernel for few rows."""
+        if activation not in self.ACTIVATIONS:
+            raise KernelError(f"gate_up_act: activation {activation!r} is not known ({', '.join(self.ACTIVATIONS)})")
         M, K = x.shape
         if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[0] % 2 == 0 \
                 and self._use_decode_gemm(M, weight.shape[0], K, True):
             if norm is not None and not self._can_fuse_norm(x, norm):
                 x, norm = self.rmsnorm(x, *norm), None
-            return self.linear_decode(x, weight, gated=True, norm=norm)
+            return self.linear_decode(x, weight, gated=True, norm=norm, activation=activation)
         if norm is not None:
             x = self.rmsnorm(x, *norm)
         if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and self._tcgen05_fills(M, weight.shape[0], True) \
                 and K % 8 == 0 and weight.shape[0] % 2 == 0:
-            return self.linear_tcgen05(x, weight, gated=True)
-        return self.silu_mul(self.linear(x, weight))
+            return self.linear_tcgen05(x, weight, gated=True, activation=activation)
+        if activation == "silu":
+            return self.silu_mul(self.linear(x, weight))
+        # the product leaves its kernel in float; the activation kernel rounds once
+        return self.act_mul(self.linear(x, weight, out_dtype=torch.float32), activation, x.dtype)
 
     # ------------------------------------------------------------------ output-norm layers, gated attention, state-space mixer
     def residual_rmsnorm(self, y, gamma, eps: float, residual: Optional[torch.Tensor], rounded_dtype=None,
@@ -855,13 +865,6 @@ class CudaKernels:
                                                c_int(gate_up.shape[0]), c_int(inter), c_int(self.ACTIVATIONS[activation]), self._stream())
         _check("act_mul", st)
         return out
-
-    def gate_up_act(self, x, weight, activation: str, out_dtype=None) -> torch.Tensor:
-        """act(x Wg^T) * (x Wu^T) for weight rows [Wg | Wu].  SiLU takes the fused kernels of `gate_up_silu`; other
-        activations run the product with a float32 result and the activation kernel, which rounds once."""
-        if activation == "silu" and (out_dtype is None or out_dtype == x.dtype):
-            return self.gate_up_silu(x, weight)
-        return self.act_mul(self.linear(x, weight, out_dtype=torch.float32), activation, out_dtype or x.dtype)
 
     def qk_norm_rope_cache_write(self, proj, q_gamma, k_gamma, eps: float, positions, cos, sin, slot_mapping, cache_layer,
                                  num_heads, num_kv_heads, head_dim, out_dtype, with_gate: bool = False, write_kv: bool = True):

@@ -33,9 +33,7 @@ class GatedMLP(Part):
         if self.activation == "silu":
             h = ctx.kernels.gate_up_silu(x, self.gate_up.weight, norm=input_norm)
         else:
-            if input_norm is not None:
-                x = ctx.kernels.rmsnorm(x, *input_norm)
-            h = ctx.kernels.gate_up_act(x, self.gate_up.weight, self.activation)
+            h = ctx.kernels.gate_up_act(x, self.gate_up.weight, self.activation, norm=input_norm)
         return self.down(h, ctx, residual=residual, out_dtype=out_dtype)
 
 

@@ -45,7 +45,7 @@ class RotaryEncoding(Part):
     rotate in a GEMM's epilogue (whole heads only) leave such a model to the rotary kernel."""
 
     def __init__(self, head_dim: int, theta: float, scaling: Optional[dict] = None, rotary_dim: Optional[int] = None):
-        if head_dim % 2:
+        if head_dim % 2 and rotary_dim is None:
             raise ConfigError(f"rotary encoding needs an even head_dim, got {head_dim}")
         rotary_dim = head_dim if rotary_dim is None else rotary_dim
         if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:

@@ -43,8 +43,8 @@ class EmulatedKernels:
             a = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
         return (a * u).to(out_dtype or gate_up.dtype)
 
-    def gate_up_act(self, x, weight, activation, out_dtype=None):
-        return self.act_mul(self.linear(x, weight, out_dtype=torch.float32), activation, out_dtype or x.dtype)
+    def gate_up_act(self, x, weight, activation="silu", norm=None):
+        return self.act_mul(self.linear(x, weight, out_dtype=torch.float32, norm=norm), activation, x.dtype)
 
     def qk_norm_rope_cache_write(self, proj, q_gamma, k_gamma, eps, positions, cos, sin, slot_mapping, cache_layer,
                                  num_heads, num_kv_heads, head_dim, out_dtype, with_gate=False, write_kv=True):

@@ -56,6 +56,20 @@ def test_gelu_gated_product(K, dtype):
     assert rel_err(got, P.gelu_tanh(h[:, :48]) * h[:, 48:]) < TOL[dtype]
 
 
+@pytest.mark.parametrize("rows", [1, 8, 40, 64, 130, 300, 1024])
+def test_gelu_in_the_gated_gemm_epilogues(K, rows):
+    """bfloat16 rows through the dispatch a model takes: the weight-streaming GEMM for few rows, the prefill GEMM for many
+    (both apply the activation to their float accumulators), the product and the activation kernel in between."""
+    x, w = rnd(rows, 256, seed=90).to(torch.bfloat16), rnd(2 * 384, 256, seed=91, scale=0.15).to(torch.bfloat16)
+    h = x.double() @ w.double().t()
+    want = P.gelu_tanh(h[:, :384]) * h[:, 384:]
+    got = K.gate_up_act(x.cuda(), w.cuda(), "gelu_tanh")
+    assert got.dtype == torch.bfloat16 and rel_err(got, want) < 6e-3
+    silu = K.gate_up_act(x.cuda(), w.cuda(), "silu")
+    assert rel_err(silu, P.silu(h[:, :384]) * h[:, 384:]) < 6e-3 and rel_err(silu, want) > 2e-2      # the two differ
+    K.raise_on_abort()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(6, 2, 32, 16), (8, 2, 64, 64), (3, 3, 24, 2), (4, 1, 128, 96)])
 def test_qk_norm_rotation_cache_write(K, dtype, nh, nkv, hd, rot):
@@ -151,11 +165,13 @@ def test_tensor_core_attention_paths_with_cap_sink_gate(K, hd, page):
                                            K.decode_attention(q, cache, meta, o, nh, nkv, hd, scale, None, q_filter=1, **x)),
         "flash + cp.async decode": lambda o: (K.flash_attention(q, cache, meta, o, nh, nkv, hd, scale, None, mode=0, q_filter=2, **x),
                                               K.decode_attention(q, cache, meta, o, nh, nkv, hd, scale, None, q_filter=1, tma=False, **x)),
-        "flash, 3 splits": lambda o: (K.flash_attention(q, cache, meta, o, nh, nkv, hd, scale, None, mode=0, q_filter=2, **x),
-                                      K.decode_attention(q, cache, meta, o, nh, nkv, hd, scale, None, q_filter=1, num_splits=3, **x)),
-        "flash, 5 splits by cp.async": lambda o: (K.flash_attention(q, cache, meta, o, nh, nkv, hd, scale, None, mode=0, q_filter=2, **x),
-                                                  K.decode_attention(q, cache, meta, o, nh, nkv, hd, scale, None, q_filter=1, num_splits=5,
-                                                                     tma=False, **x)),
+        # (the merge of key splits writes every row of the step, so here the decoded tokens go first and the prompt
+        # portions' kernel overwrites its own rows afterwards; a model's mixed steps do not split)
+        "3 splits, then flash": lambda o: (K.decode_attention(q, cache, meta, o, nh, nkv, hd, scale, None, q_filter=1, num_splits=3, **x),
+                                           K.flash_attention(q, cache, meta, o, nh, nkv, hd, scale, None, mode=0, q_filter=2, **x)),
+        "5 splits by cp.async, then flash": lambda o: (K.decode_attention(q, cache, meta, o, nh, nkv, hd, scale, None, q_filter=1,
+                                                                          num_splits=5, tma=False, **x),
+                                                       K.flash_attention(q, cache, meta, o, nh, nkv, hd, scale, None, mode=0, q_filter=2, **x)),
     }.items():
         o = torch.full_like(q, float("nan"))
         run(o)

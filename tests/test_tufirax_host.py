@@ -57,10 +57,10 @@ def test_config_problems_are_collected():
     text = str(e.value)
     for piece in ("vdim", "rot.dims", "groups", "'conv'", "weights_of"):
         assert piece in text, (piece, text)
-    other = X.small_a()
-    other["layers"][2]["mixer"]["softcap"] = 3.0    # a borrowing layer must describe its source
-    with pytest.raises(ConfigError, match="different layer"):
-        config_from_dict(other)
+    loop = X.small_a()
+    loop["layers"][1]["weights_of"] = 2             # 1 -> 2 -> 1
+    with pytest.raises(ConfigError, match="circle"):
+        config_from_dict(loop)
 
 
 def test_architecture_key_forms():
@@ -150,6 +150,24 @@ def test_replay_matches_plain_under_every_cut(emulated, tmp_path, which, schedul
     assert not engine.cache.requests and engine.cache.slots.num_free == 4
 
 
+@pytest.mark.parametrize("kind", ["mamba2", "attention"])
+def test_models_of_one_kind_of_layer(emulated, kind):
+    """Only state (no page group at all) or only pages (no state): the engine asks for nothing it does not need."""
+    from rvllm_b200.engine.step import StepEntry
+    layer = X.mamba2(ff=40) if kind == "mamba2" else X.attention(heads=2, kv_heads=1, dim=16, rot_dims=8)
+    folder = X.write_folder(X.config([layer, X.shared(layer, 0)], width=48, vocab=97), seed=2, edit=X.lively)
+    toks = random_requests(97, (29,), seed=1)["r0"]
+    want = X.plain_logits(folder, {"x": toks})["x"]
+    engine = trace_mod.build_engine(folder, "float32", 64, block_size=8, device="cpu")
+    assert (len(engine.cache.groups), len(engine.cache._state)) == ((0, 2) if kind == "mamba2" else (1, 0))
+    got = [engine.runner.step([StepEntry("x", toks[:11], list(range(11)))]), engine.runner.step([StepEntry("x", toks[11:28], list(range(17)))]),
+           engine.runner.step([StepEntry("x", toks[28:], [0])])]
+    got = torch.cat(got).double()
+    assert float((got - want).abs().max() / want.abs().max()) < 2e-5
+    engine.runner.finish("x")
+    engine.cache.check()
+
+
 def test_state_slot_is_cleared_for_its_next_request(emulated):
     """Two requests, one after the other, in an engine with ONE slot: the second starts from a zero state."""
     folder, vocab, reqs, ref = _reference("a")
@@ -174,3 +192,27 @@ def test_generate_greedy_matches_plain(emulated):
     for p, o in zip(prompts, outs):
         assert o.outputs[0].token_ids == P.greedy(cfg, w, p, 6)
     assert not llm.engine.cache.requests
+
+
+def test_command_line_info_and_random_weights(tmp_path):
+    """`rvllm random-weights` writes a folder for the design from a config.json; `rvllm info` reads it back."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(X.small_a()))
+    out = tmp_path / "model"
+    run = lambda *a: subprocess.run([sys.executable, os.path.join(root, "bin", "rvllm"), *a], capture_output=True, text=True, timeout=300)
+    p = run("random-weights", "--config", str(cfg_file), "--out", str(out), "--seed", "3")
+    assert p.returncode == 0, p.stderr
+    p = run("info", "--model", str(out))
+    assert p.returncode == 0, p.stderr
+    info = json.loads(p.stdout)
+    assert info["architecture"] == "Tufirax" and info["config"]["layers"][2]["weights_of"] == 1
+    # two mamba2 layers of (6 heads x 24 x 20 + 2 x 264) floats, one of (4 x 40 x 33 + 4 x 212)
+    assert info["state_bytes_per_request"] == 4 * (2 * (6 * 24 * 20 + 2 * 264) + (4 * 40 * 33 + 4 * 212))
+    assert info["kv_bytes_per_token_bf16"] == 2 * (2 * 2 * 32 * 2)            # two attention layers: k and v of 2 heads of 32
+    cfg, w = X.read_folder(str(out))
+    assert P.forward(cfg, w, [1, 2, 3]).shape == (3, 211)
