@@ -53,6 +53,54 @@ causal_conv_silu_kernel(const void* __restrict__ in, int in_dtype, int in_stride
     rv_store_any(out, out_dtype, (size_t)t * channels + c, acc / (1.0f + expf(-acc)));
 }
 
+// The same for up to four taps, RV_CONV_TOKENS consecutive tokens per thread: the last taps - 1 inputs stay in registers
+// from token to token, so a token costs one load; where a new sequence begins inside the thread's run the registers
+// are filled again from the rows before it or from the request's state.
+#define RV_CONV_TOKENS 8
+template <int TAPS>
+__global__ void __launch_bounds__(256)
+causal_conv_silu_run_kernel(const void* __restrict__ in, int in_dtype, int in_stride, int col0,
+                            const void* __restrict__ w, const void* __restrict__ bias, int w_dtype,
+                            const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
+                            const int* __restrict__ state_slots, const float* __restrict__ state, size_t state_stride,
+                            size_t conv_off, void* __restrict__ out, int out_dtype, int n_tokens, int channels) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int t_begin = blockIdx.y * RV_CONV_TOKENS;
+    const int t_end = t_begin + RV_CONV_TOKENS < n_tokens ? t_begin + RV_CONV_TOKENS : n_tokens;
+    float wt[TAPS], win[TAPS > 1 ? TAPS - 1 : 1];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wt[j] = rv_load_param(w, w_dtype, c * TAPS + j);
+    const float b = bias ? rv_load_param(bias, w_dtype, c) : 0.f;
+    int seq_end = -1;
+    for (int t = t_begin; t < t_end; ++t) {
+        if (t >= seq_end) {                            // the thread's first token, or the first of another sequence
+            const int seq = token_seq[t];
+            const int start = cu_seqlens[seq];
+            seq_end = cu_seqlens[seq + 1];
+            const int slot = state_slots[seq];
+            const float* hist = slot >= 0 ? state + (size_t)slot * state_stride + conv_off : nullptr;
+#pragma unroll
+            for (int k = 0; k < TAPS - 1; ++k) {
+                const int idx = (t - start) - (TAPS - 1) + k;
+                win[k] = idx >= 0 ? rv_load_any(in, in_dtype, (size_t)(start + idx) * in_stride + col0 + c)
+                                  : (hist ? hist[(size_t)(TAPS - 1 + idx) * channels + c] : 0.f);
+            }
+        }
+        const float v = rv_load_any(in, in_dtype, (size_t)t * in_stride + col0 + c);
+        float acc = b;
+#pragma unroll
+        for (int k = 0; k < TAPS - 1; ++k) acc = fmaf(wt[k], win[k], acc);
+        acc = fmaf(wt[TAPS - 1], v, acc);
+#pragma unroll
+        for (int k = 0; k + 1 < TAPS - 1; ++k) win[k] = win[k + 1];
+        if (TAPS > 1) win[TAPS - 2] = v;
+        rv_store_any(out, out_dtype, (size_t)t * channels + c, acc / (1.0f + expf(-acc)));
+    }
+}
+
 // After the convolution of a step: the state becomes the last taps - 1 inputs of each sequence.
 __global__ void __launch_bounds__(256)
 conv_state_update_kernel(const void* __restrict__ in, int in_dtype, int in_stride, int col0,
@@ -92,6 +140,19 @@ RV_EXPORT int rv_causal_conv_silu(const void* in, int in_dtype, int in_stride, i
     if (n_tokens > 65535 * 8 || n_seqs > 65535) return RV_ERR_BAD_SIZE;
     const int threads = channels >= 256 ? 256 : 128;
     const int bx = (channels + threads - 1) / threads;
+    if (taps <= 4) {
+        const dim3 grid(bx, (n_tokens + RV_CONV_TOKENS - 1) / RV_CONV_TOKENS);
+#define RV_CONV_LAUNCH(TAPS)                                                                                                          \
+        RV_LAUNCH_ST = rv_launch(causal_conv_silu_run_kernel<TAPS>, dim3(grid), dim3(threads), 0, stream, in, in_dtype, in_stride, col0, w, \
+                                 bias, w_dtype, token_seq, cu_seqlens, state_slots, (const float*)state, (size_t)state_stride,        \
+                                 (size_t)conv_off, out, out_dtype, n_tokens, channels)
+        if (taps == 1) RV_CONV_LAUNCH(1);
+        else if (taps == 2) RV_CONV_LAUNCH(2);
+        else if (taps == 3) RV_CONV_LAUNCH(3);
+        else RV_CONV_LAUNCH(4);
+#undef RV_CONV_LAUNCH
+        if (RV_LAUNCH_ST != RV_OK) return rv_launch_status();
+    } else
     for (int t0 = 0; t0 < n_tokens; t0 += 65535) {          // (gridDim.y is limited)
         const int nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
         RV_LAUNCH_ST = rv_launch(causal_conv_silu_kernel, dim3(bx, nt), dim3(threads), 0, stream,
@@ -108,13 +169,15 @@ RV_EXPORT int rv_causal_conv_silu(const void* in, int in_dtype, int in_stride, i
 
 // ------------------------------------------------------------------ the recurrence
 // Grid (P / 32 column blocks, heads, sequences); 128 threads = 32 columns p x 4 slices of the state dimension: thread
-// (p, s) keeps S[n][p] for n = 4 i + s in registers and the four slices of a column add their parts of y with shuffles.
-// The tokens of a sequence are walked in chunks of RV_SCAN_CHUNK: B, C, the decay and dt x of a chunk are staged in
-// shared memory, then the chunk runs without a barrier per token.
+// (p, s) keeps S[n][p] for the NPT consecutive n of its slice in registers, and the four slices of a column add their
+// parts of y with shuffles.  The tokens of a sequence are walked in chunks of RV_SCAN_CHUNK: B, C, the decay and dt x of
+// a chunk are staged in shared memory (as floats, a slice's part of a row padded by four so that the slices' 16-byte
+// reads fall into different banks), then the chunk runs without a barrier per token.  Where the rows allow 16-byte
+// loads (bfloat16, sizes that are multiples of 8) the next chunk is fetched into registers before the current one is
+// computed, so that its way from memory is hidden behind the arithmetic.
 #define RV_SCAN_CHUNK 16
-#define RV_SCAN_COLS 32
 
-template <int NPT>
+template <int NPT, int NSL>
 __global__ void __launch_bounds__(128)
 ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,           // [T, channels]: x | B | C after the convolution
                 const void* __restrict__ dt_in, int dt_dtype, int dt_stride, int dt_col0,   // raw dt: column dt_col0 + h of rows of dt_stride
@@ -124,23 +187,28 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
                 int heads, int P, int N, int groups) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
-    extern __shared__ float sm[];
-    float* sB = sm;                                   // [chunk][N]
-    float* sC = sB + RV_SCAN_CHUNK * N;               // [chunk][N]
-    float* sX = sC + RV_SCAN_CHUNK * N;               // [chunk][32]   dt * x
-    float* sY = sX + RV_SCAN_CHUNK * RV_SCAN_COLS;    // [chunk][32]
-    float* sDec = sY + RV_SCAN_CHUNK * RV_SCAN_COLS;  // [chunk]       exp(-exp(A_log) dt)
+    constexpr int COLS = 128 / NSL;                   // columns p of a block
+    constexpr int SEG = NPT + 4, TOK = NSL * SEG;     // floats of a slice's part, and of a token's B (or C)
+    constexpr int PRE = NSL * NPT >= 32 ? NSL * NPT / 32 : 1;   // 16-byte pieces of a chunk's B and C per thread
+    constexpr int XV = COLS / 8;                      // 16-byte pieces of a token's x
+    extern __shared__ __align__(16) float sm[];
+    float* sB = sm;                                   // [chunk][TOK]
+    float* sC = sB + RV_SCAN_CHUNK * TOK;             // [chunk][TOK]
+    float* sX = sC + RV_SCAN_CHUNK * TOK;             // [chunk][32]   x
+    float* sY = sX + RV_SCAN_CHUNK * COLS;    // [chunk][32]
+    float* sDec = sY + RV_SCAN_CHUNK * COLS;  // [chunk]       exp(-exp(A_log) dt)
     float* sDt = sDec + RV_SCAN_CHUNK;                // [chunk]
-    const int seq = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * RV_SCAN_COLS;
+    const int tid = threadIdx.x;
+    const int seq = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * COLS;
     const int start = cu_seqlens[seq], n_tok = cu_seqlens[seq + 1] - start;
     const int slot = state_slots[seq];
     const int inner = heads * P;
-    const int lane_p = threadIdx.x >> 2, slice = threadIdx.x & 3;
+    const int lane_p = tid / NSL, slice = tid % NSL;
     const int p = p0 + lane_p;
     const bool p_ok = p < P;
     if (slot < 0) {                                    // a padding row: no state; its output is zero
-        for (int i = threadIdx.x; i < n_tok * RV_SCAN_COLS; i += blockDim.x) {
-            const int tk = i / RV_SCAN_COLS, pp = p0 + (i - tk * RV_SCAN_COLS);
+        for (int i = tid; i < n_tok * COLS; i += blockDim.x) {
+            const int tk = i / COLS, pp = p0 + (i - tk * COLS);
             if (pp < P) y[(size_t)(start + tk) * inner + h * P + pp] = 0.f;
         }
         return;
@@ -153,83 +221,183 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
     float s[NPT];
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
-        const int n = 4 * i + slice;
+        const int n = slice * NPT + i;
         s[i] = (p_ok && n < N) ? S[(size_t)n * P + p] : 0.f;
     }
+    for (int i = tid; i < 2 * RV_SCAN_CHUNK * TOK; i += blockDim.x) sm[i] = 0.f;      // state indices beyond N stay zero
     const size_t b_col = (size_t)inner + (size_t)g * N, c_col = (size_t)inner + (size_t)groups * N + (size_t)g * N;
+    const bool vec = x_dtype == RV_DTYPE_BF16 && !(N & 7) && !(inner & 7) && !((groups * N) & 7) && !(channels & 7) && !(P & 7) &&
+                     (reinterpret_cast<uintptr_t>(xbc) & 15) == 0;
+    const int vpr = N >> 3;                            // 16-byte pieces per row of B (or C)
+    uint4 pre_bc[PRE];
+    uint4 pre_x = make_uint4(0, 0, 0, 0);
+    float pre_dt = 0.f;
+    const __nv_bfloat16* xb = (const __nv_bfloat16*)xbc;
+
+    auto fetch = [&](int t0) {                         // the chunk's rows into registers (vector path only)
+        const int nt = n_tok - t0 < RV_SCAN_CHUNK ? n_tok - t0 : RV_SCAN_CHUNK;
+#pragma unroll
+        for (int j = 0; j < PRE; ++j) {
+            const int v = tid + j * 128;
+            if (v < nt * vpr * 2) {
+                const int tk = v / (2 * vpr), r = v - tk * 2 * vpr;
+                const int which = r >= vpr, k = r - which * vpr;
+                pre_bc[j] = *reinterpret_cast<const uint4*>(xb + (size_t)(start + t0 + tk) * channels + (which ? c_col : b_col) + k * 8);
+            }
+        }
+        if (tid < nt * XV) {
+            const int tk = tid / XV, k = tid % XV;
+            const int col = h * P + p0 + k * 8;
+            pre_x = col + 8 <= channels ? *reinterpret_cast<const uint4*>(xb + (size_t)(start + t0 + tk) * channels + col) : make_uint4(0, 0, 0, 0);
+        }
+        if (tid >= 64 && tid < 64 + nt)
+            pre_dt = rv_load_any(dt_in, dt_dtype, (size_t)(start + t0 + tid - 64) * dt_stride + dt_col0 + h);
+    };
+    auto stage = [&](int t0) {                         // registers -> shared memory, as floats
+        const int nt = n_tok - t0 < RV_SCAN_CHUNK ? n_tok - t0 : RV_SCAN_CHUNK;
+#pragma unroll
+        for (int j = 0; j < PRE; ++j) {
+            const int v = tid + j * 128;
+            if (v < nt * vpr * 2) {
+                const int tk = v / (2 * vpr), r = v - tk * 2 * vpr;
+                const int which = r >= vpr, k = r - which * vpr;
+                const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&pre_bc[j]);
+                float* dst = (which ? sC : sB) + tk * TOK;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int n = k * 8 + q;
+                    dst[(n / NPT) * SEG + (n % NPT)] = __bfloat162float(e[q]);
+                }
+            }
+        }
+        if (tid < nt * XV) {
+            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&pre_x);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) sX[(tid / XV) * COLS + (tid % XV) * 8 + q] = __bfloat162float(e[q]);
+        }
+        if (tid >= 64 && tid < 64 + nt) {
+            const float raw = pre_dt + bias;
+            const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+            sDt[tid - 64] = dt;
+            sDec[tid - 64] = expf(A * dt);
+        }
+    };
+    auto stage_plain = [&](int t0) {                   // any type and size: element by element, four loads in flight
+        const int nt = n_tok - t0 < RV_SCAN_CHUNK ? n_tok - t0 : RV_SCAN_CHUNK;
+        if (tid < nt) {
+            const float raw = rv_load_any(dt_in, dt_dtype, (size_t)(start + t0 + tid) * dt_stride + dt_col0 + h) + bias;
+            const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+            sDt[tid] = dt;
+            sDec[tid] = expf(A * dt);
+        }
+#pragma unroll 4
+        for (int i = tid; i < nt * N; i += 128) {
+            const int tk = i / N, n = i - tk * N;
+            const size_t rowb = (size_t)(start + t0 + tk) * channels;
+            const int at = tk * TOK + (n / NPT) * SEG + (n % NPT);
+            sB[at] = rv_load_any(xbc, x_dtype, rowb + b_col + n);
+            sC[at] = rv_load_any(xbc, x_dtype, rowb + c_col + n);
+        }
+#pragma unroll 4
+        for (int i = tid; i < nt * COLS; i += 128) {
+            const int tk = i / COLS, pp = p0 + (i - tk * COLS);
+            sX[i] = pp < P ? rv_load_any(xbc, x_dtype, (size_t)(start + t0 + tk) * channels + h * P + pp) : 0.f;
+        }
+    };
+
+    if (vec && n_tok > 0) fetch(0);
     for (int t0 = 0; t0 < n_tok; t0 += RV_SCAN_CHUNK) {
         const int nt = n_tok - t0 < RV_SCAN_CHUNK ? n_tok - t0 : RV_SCAN_CHUNK;
         __syncthreads();                               // the chunk before has been read (and its sY written out)
-        if (threadIdx.x < nt) {
-            const int tk = threadIdx.x;
-            const float raw = rv_load_any(dt_in, dt_dtype, (size_t)(start + t0 + tk) * dt_stride + dt_col0 + h) + bias;
-            const float dt = raw > 20.f ? raw : log1pf(expf(raw));
-            sDt[tk] = dt;
-            sDec[tk] = expf(A * dt);
-        }
-        for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
-            const int tk = i / N, n = i - tk * N;
-            const size_t rowb = (size_t)(start + t0 + tk) * channels;
-            sB[tk * N + n] = rv_load_any(xbc, x_dtype, rowb + b_col + n);
-            sC[tk * N + n] = rv_load_any(xbc, x_dtype, rowb + c_col + n);
-        }
-        for (int i = threadIdx.x; i < nt * RV_SCAN_COLS; i += blockDim.x) {
-            const int tk = i / RV_SCAN_COLS, pp = p0 + (i - tk * RV_SCAN_COLS);
-            sX[i] = pp < P ? rv_load_any(xbc, x_dtype, (size_t)(start + t0 + tk) * channels + h * P + pp) : 0.f;
-        }
+        if (vec) stage(t0); else stage_plain(t0);
         __syncthreads();
-        for (int tk = 0; tk < nt; ++tk) {
+        if (vec && t0 + RV_SCAN_CHUNK < n_tok) fetch(t0 + RV_SCAN_CHUNK);
+        auto token = [&](int tk) {
             const float dec = sDec[tk];
-            const float xv = sX[tk * RV_SCAN_COLS + lane_p];
+            const float xv = sX[tk * COLS + lane_p];
             const float dx = sDt[tk] * xv;
-            const float* Bt = sB + tk * N;
-            const float* Ct = sC + tk * N;
-            float acc = 0.f;
+            const float4* B4 = reinterpret_cast<const float4*>(sB + tk * TOK + slice * SEG);
+            const float4* C4 = reinterpret_cast<const float4*>(sC + tk * TOK + slice * SEG);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < NPT; ++i) {
-                const int n = 4 * i + slice;
-                if (n < N) {
-                    s[i] = fmaf(dec, s[i], dx * Bt[n]);
-                    acc = fmaf(s[i], Ct[n], acc);
-                }
+            for (int j = 0; j < NPT / 4; ++j) {
+                const float4 b = B4[j], c = C4[j];
+                s[4 * j] = fmaf(dec, s[4 * j], dx * b.x);         a0 = fmaf(s[4 * j], c.x, a0);
+                s[4 * j + 1] = fmaf(dec, s[4 * j + 1], dx * b.y); a1 = fmaf(s[4 * j + 1], c.y, a1);
+                s[4 * j + 2] = fmaf(dec, s[4 * j + 2], dx * b.z); a2 = fmaf(s[4 * j + 2], c.z, a2);
+                s[4 * j + 3] = fmaf(dec, s[4 * j + 3], dx * b.w); a3 = fmaf(s[4 * j + 3], c.w, a3);
             }
+            float acc = (a0 + a1) + (a2 + a3);
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (slice == 0) sY[tk * RV_SCAN_COLS + lane_p] = fmaf(Dh, xv, acc);
+            if (NSL == 8) acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (slice == 0) sY[tk * COLS + lane_p] = fmaf(Dh, xv, acc);
+        };
+        if (nt == RV_SCAN_CHUNK) {                      // a whole chunk: unrolled, so that a token's loads overlap the one before
+#pragma unroll 4
+            for (int tk = 0; tk < RV_SCAN_CHUNK; ++tk) token(tk);
+        } else {
+            for (int tk = 0; tk < nt; ++tk) token(tk);
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * RV_SCAN_COLS; i += blockDim.x) {
-            const int tk = i / RV_SCAN_COLS, pp = p0 + (i - tk * RV_SCAN_COLS);
+        for (int i = tid; i < nt * COLS; i += blockDim.x) {
+            const int tk = i / COLS, pp = p0 + (i - tk * COLS);
             if (pp < P) y[(size_t)(start + t0 + tk) * inner + h * P + pp] = sY[i];
         }
     }
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
-        const int n = 4 * i + slice;
+        const int n = slice * NPT + i;
         if (p_ok && n < N) S[(size_t)n * P + p] = s[i];
     }
+}
+
+template <int NPT, int NSL>
+static int launch_scan(cudaStream_t stream, const void* xbc, int x_dtype, int channels, const void* dt_in, int dt_dtype,
+                       int dt_stride, int dt_col0, const void* dt_bias, const void* a_log, const void* d_skip, int p_dtype,
+                       const int* cu_seqlens, const int* state_slots, float* state, size_t state_stride, float* y, int n_seqs,
+                       int heads, int P, int N, int groups) {
+    constexpr int COLS = 128 / NSL;
+    const dim3 grid((P + COLS - 1) / COLS, heads, n_seqs);
+    const size_t smem = sizeof(float) * ((size_t)2 * RV_SCAN_CHUNK * NSL * (NPT + 4) + 2 * RV_SCAN_CHUNK * COLS + 2 * RV_SCAN_CHUNK);
+    static RvPerDevice configured;
+    if (smem > 48 * 1024)
+        if (int e = rv_configure_smem(configured, ssm_scan_kernel<NPT, NSL>, (int)smem)) return e;
+    return rv_launch(ssm_scan_kernel<NPT, NSL>, grid, dim3(128), smem, stream, xbc, x_dtype, channels, dt_in, dt_dtype, dt_stride, dt_col0,
+                     dt_bias, a_log, d_skip, p_dtype, cu_seqlens, state_slots, state, state_stride, y, heads, P, N, groups);
 }
 
 RV_EXPORT int rv_ssm_scan(const void* xbc, int x_dtype, int channels, const void* dt_in, int dt_dtype, int dt_stride, int dt_col0,
                           const void* dt_bias, const void* a_log, const void* d_skip, int p_dtype, const int* cu_seqlens,
                           const int* state_slots, float* state, long long state_stride, float* y, int n_seqs, int heads, int P,
-                          int N, int groups, cudaStream_t stream) {
+                          int N, int groups, int slices, cudaStream_t stream) {
     if (n_seqs < 0 || heads <= 0 || P <= 0 || N <= 0 || groups <= 0 || heads % groups) return RV_ERR_BAD_SIZE;
     if (channels < heads * P + 2 * groups * N || dt_stride < dt_col0 + heads || dt_col0 < 0) return RV_ERR_BAD_SIZE;
     if ((x_dtype | dt_dtype | p_dtype) & ~1) return RV_ERR_BAD_DTYPE;
     if (N > 256 || heads > 65535 || n_seqs > 65535) return RV_ERR_UNSUPPORTED;
     if (n_seqs == 0) return RV_OK;
-    const dim3 grid((P + RV_SCAN_COLS - 1) / RV_SCAN_COLS, heads, n_seqs);
-    const size_t smem = sizeof(float) * ((size_t)2 * RV_SCAN_CHUNK * N + 2 * RV_SCAN_CHUNK * RV_SCAN_COLS + 2 * RV_SCAN_CHUNK);
-#define RV_SCAN_LAUNCH(NPT)                                                                                                  \
-    RV_LAUNCH_ST = rv_launch(ssm_scan_kernel<NPT>, dim3(grid), dim3(128), smem, stream, xbc, x_dtype, channels, dt_in, dt_dtype, \
-                             dt_stride, dt_col0, dt_bias, a_log, d_skip, p_dtype, cu_seqlens, state_slots, state,           \
-                             (size_t)state_stride, y, heads, P, N, groups)
-    if (N <= 16) RV_SCAN_LAUNCH(4);
-    else if (N <= 32) RV_SCAN_LAUNCH(8);
-    else if (N <= 64) RV_SCAN_LAUNCH(16);
-    else if (N <= 128) RV_SCAN_LAUNCH(32);
-    else RV_SCAN_LAUNCH(64);
+    // eight slices of the state dimension and 16 columns per block only where blocks of 32 columns would leave half of the SMs
+    // without one (measured: with 256 blocks of 32 columns on 148 SMs the finer cut is 1.5 x slower - every thread then reads
+    // its B and C from shared memory for half as many columns)
+    // (`slices` 4 or 8 overrides the choice)
+    if (slices != 0 && slices != 4 && slices != 8) return RV_ERR_BAD_SIZE;
+    if (slices == 4 && N > 256) return RV_ERR_UNSUPPORTED;
+    const bool fine = slices ? slices == 8 : 2LL * ((P + 31) / 32) * heads * n_seqs <= (long long)rv_sm_count();
+#define RV_SCAN_LAUNCH(NPT, NSL)                                                                                                 \
+    RV_LAUNCH_ST = launch_scan<NPT, NSL>(stream, xbc, x_dtype, channels, dt_in, dt_dtype, dt_stride, dt_col0, dt_bias, a_log,    \
+                                         d_skip, p_dtype, cu_seqlens, state_slots, state, (size_t)state_stride, y, n_seqs, heads, P, N, groups)
+    if (fine) {
+        if (N <= 32) RV_SCAN_LAUNCH(4, 8);
+        else if (N <= 64) RV_SCAN_LAUNCH(8, 8);
+        else if (N <= 128) RV_SCAN_LAUNCH(16, 8);
+        else RV_SCAN_LAUNCH(32, 8);
+    } else {
+        if (N <= 16) RV_SCAN_LAUNCH(4, 4);
+        else if (N <= 32) RV_SCAN_LAUNCH(8, 4);
+        else if (N <= 64) RV_SCAN_LAUNCH(16, 4);
+        else if (N <= 128) RV_SCAN_LAUNCH(32, 4);
+        else RV_SCAN_LAUNCH(64, 4);
+    }
 #undef RV_SCAN_LAUNCH
     return rv_launch_status();
 }
