@@ -177,7 +177,7 @@ RV_EXPORT int rv_causal_conv_silu(const void* in, int in_dtype, int in_stride, i
 // computed, so that its way from memory is hidden behind the arithmetic.
 #define RV_SCAN_CHUNK 16
 
-template <int NPT, int NSL>
+template <int NPT, int NC>
 __global__ void __launch_bounds__(128)
 ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,           // [T, channels]: x | B | C after the convolution
                 const void* __restrict__ dt_in, int dt_dtype, int dt_stride, int dt_col0,   // raw dt: column dt_col0 + h of rows of dt_stride
@@ -187,7 +187,8 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
                 int heads, int P, int N, int groups) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
-    constexpr int COLS = 128 / NSL;                   // columns p of a block
+    constexpr int NSL = 8;                            // slices of the state dimension
+    constexpr int COLS = NC * 128 / NSL;              // columns p of a block
     constexpr int SEG = NPT + 4, TOK = NSL * SEG;     // floats of a slice's part, and of a token's B (or C)
     constexpr int PRE = NSL * NPT >= 32 ? NSL * NPT / 32 : 1;   // 16-byte pieces of a chunk's B and C per thread
     constexpr int XV = COLS / 8;                      // 16-byte pieces of a token's x
@@ -203,9 +204,8 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
     const int start = cu_seqlens[seq], n_tok = cu_seqlens[seq + 1] - start;
     const int slot = state_slots[seq];
     const int inner = heads * P;
-    const int lane_p = tid / NSL, slice = tid % NSL;
+    const int lane_p = (tid / NSL) * NC, slice = tid % NSL;      // the thread's first column within the block
     const int p = p0 + lane_p;
-    const bool p_ok = p < P;
     if (slot < 0) {                                    // a padding row: no state; its output is zero
         for (int i = tid; i < n_tok * COLS; i += blockDim.x) {
             const int tk = i / COLS, pp = p0 + (i - tk * COLS);
@@ -218,12 +218,14 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
     const float bias = rv_load_param(dt_bias, p_dtype, h);
     const float Dh = rv_load_param(d_skip, p_dtype, h);
     float* S = state + (size_t)slot * state_stride + (size_t)h * N * P;
-    float s[NPT];
+    float s[NC][NPT];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-        const int n = slice * NPT + i;
-        s[i] = (p_ok && n < N) ? S[(size_t)n * P + p] : 0.f;
-    }
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int n = slice * NPT + i;
+            s[c][i] = (p + c < P && n < N) ? S[(size_t)n * P + p + c] : 0.f;
+        }
     for (int i = tid; i < 2 * RV_SCAN_CHUNK * TOK; i += blockDim.x) sm[i] = 0.f;      // state indices beyond N stay zero
     const size_t b_col = (size_t)inner + (size_t)g * N, c_col = (size_t)inner + (size_t)groups * N + (size_t)g * N;
     const bool vec = x_dtype == RV_DTYPE_BF16 && !(N & 7) && !(inner & 7) && !((groups * N) & 7) && !(channels & 7) && !(P & 7) &&
@@ -313,25 +315,35 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
         __syncthreads();
         if (vec && t0 + RV_SCAN_CHUNK < n_tok) fetch(t0 + RV_SCAN_CHUNK);
         auto token = [&](int tk) {
-            const float dec = sDec[tk];
-            const float xv = sX[tk * COLS + lane_p];
-            const float dx = sDt[tk] * xv;
+            const float dec = sDec[tk], dtv = sDt[tk];
             const float4* B4 = reinterpret_cast<const float4*>(sB + tk * TOK + slice * SEG);
             const float4* C4 = reinterpret_cast<const float4*>(sC + tk * TOK + slice * SEG);
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            float xv[NC], dx[NC], acc[NC][4];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                xv[c] = sX[tk * COLS + lane_p + c];
+                dx[c] = dtv * xv[c];
+                acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+            }
 #pragma unroll
             for (int j = 0; j < NPT / 4; ++j) {
-                const float4 b = B4[j], c = C4[j];
-                s[4 * j] = fmaf(dec, s[4 * j], dx * b.x);         a0 = fmaf(s[4 * j], c.x, a0);
-                s[4 * j + 1] = fmaf(dec, s[4 * j + 1], dx * b.y); a1 = fmaf(s[4 * j + 1], c.y, a1);
-                s[4 * j + 2] = fmaf(dec, s[4 * j + 2], dx * b.z); a2 = fmaf(s[4 * j + 2], c.z, a2);
-                s[4 * j + 3] = fmaf(dec, s[4 * j + 3], dx * b.w); a3 = fmaf(s[4 * j + 3], c.w, a3);
+                const float4 b = B4[j], cc = C4[j];            // one read of B and C serves the thread's NC columns
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    s[c][4 * j] = fmaf(dec, s[c][4 * j], dx[c] * b.x);         acc[c][0] = fmaf(s[c][4 * j], cc.x, acc[c][0]);
+                    s[c][4 * j + 1] = fmaf(dec, s[c][4 * j + 1], dx[c] * b.y); acc[c][1] = fmaf(s[c][4 * j + 1], cc.y, acc[c][1]);
+                    s[c][4 * j + 2] = fmaf(dec, s[c][4 * j + 2], dx[c] * b.z); acc[c][2] = fmaf(s[c][4 * j + 2], cc.z, acc[c][2]);
+                    s[c][4 * j + 3] = fmaf(dec, s[c][4 * j + 3], dx[c] * b.w); acc[c][3] = fmaf(s[c][4 * j + 3], cc.w, acc[c][3]);
+                }
             }
-            float acc = (a0 + a1) + (a2 + a3);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (NSL == 8) acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (slice == 0) sY[tk * COLS + lane_p] = fmaf(Dh, xv, acc);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                float a = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
+                a += __shfl_xor_sync(0xffffffffu, a, 1);
+                a += __shfl_xor_sync(0xffffffffu, a, 2);
+                a += __shfl_xor_sync(0xffffffffu, a, 4);
+                if (slice == 0) sY[tk * COLS + lane_p + c] = fmaf(Dh, xv[c], a);
+            }
         };
         if (nt == RV_SCAN_CHUNK) {                      // a whole chunk: unrolled, so that a token's loads overlap the one before
 #pragma unroll 4
@@ -346,57 +358,55 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
         }
     }
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-        const int n = slice * NPT + i;
-        if (p_ok && n < N) S[(size_t)n * P + p] = s[i];
-    }
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int n = slice * NPT + i;
+            if (p + c < P && n < N) S[(size_t)n * P + p + c] = s[c][i];
+        }
 }
 
-template <int NPT, int NSL>
+template <int NPT, int NC>
 static int launch_scan(cudaStream_t stream, const void* xbc, int x_dtype, int channels, const void* dt_in, int dt_dtype,
                        int dt_stride, int dt_col0, const void* dt_bias, const void* a_log, const void* d_skip, int p_dtype,
                        const int* cu_seqlens, const int* state_slots, float* state, size_t state_stride, float* y, int n_seqs,
                        int heads, int P, int N, int groups) {
-    constexpr int COLS = 128 / NSL;
+    constexpr int COLS = NC * 16;
     const dim3 grid((P + COLS - 1) / COLS, heads, n_seqs);
-    const size_t smem = sizeof(float) * ((size_t)2 * RV_SCAN_CHUNK * NSL * (NPT + 4) + 2 * RV_SCAN_CHUNK * COLS + 2 * RV_SCAN_CHUNK);
+    const size_t smem = sizeof(float) * ((size_t)2 * RV_SCAN_CHUNK * 8 * (NPT + 4) + 2 * RV_SCAN_CHUNK * COLS + 2 * RV_SCAN_CHUNK);
     static RvPerDevice configured;
     if (smem > 48 * 1024)
-        if (int e = rv_configure_smem(configured, ssm_scan_kernel<NPT, NSL>, (int)smem)) return e;
-    return rv_launch(ssm_scan_kernel<NPT, NSL>, grid, dim3(128), smem, stream, xbc, x_dtype, channels, dt_in, dt_dtype, dt_stride, dt_col0,
+        if (int e = rv_configure_smem(configured, ssm_scan_kernel<NPT, NC>, (int)smem)) return e;
+    return rv_launch(ssm_scan_kernel<NPT, NC>, grid, dim3(128), smem, stream, xbc, x_dtype, channels, dt_in, dt_dtype, dt_stride, dt_col0,
                      dt_bias, a_log, d_skip, p_dtype, cu_seqlens, state_slots, state, state_stride, y, heads, P, N, groups);
 }
 
+// `columns`: columns per thread, 1 or 2; 0 lets the launcher choose by the size of the grid.
 RV_EXPORT int rv_ssm_scan(const void* xbc, int x_dtype, int channels, const void* dt_in, int dt_dtype, int dt_stride, int dt_col0,
                           const void* dt_bias, const void* a_log, const void* d_skip, int p_dtype, const int* cu_seqlens,
                           const int* state_slots, float* state, long long state_stride, float* y, int n_seqs, int heads, int P,
-                          int N, int groups, int slices, cudaStream_t stream) {
+                          int N, int groups, int columns, cudaStream_t stream) {
     if (n_seqs < 0 || heads <= 0 || P <= 0 || N <= 0 || groups <= 0 || heads % groups) return RV_ERR_BAD_SIZE;
     if (channels < heads * P + 2 * groups * N || dt_stride < dt_col0 + heads || dt_col0 < 0) return RV_ERR_BAD_SIZE;
     if ((x_dtype | dt_dtype | p_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (columns < 0 || columns > 2) return RV_ERR_BAD_SIZE;
     if (N > 256 || heads > 65535 || n_seqs > 65535) return RV_ERR_UNSUPPORTED;
     if (n_seqs == 0) return RV_OK;
-    // eight slices of the state dimension and 16 columns per block only where blocks of 32 columns would leave half of the SMs
-    // without one (measured: with 256 blocks of 32 columns on 148 SMs the finer cut is 1.5 x slower - every thread then reads
-    // its B and C from shared memory for half as many columns)
-    // (`slices` 4 or 8 overrides the choice)
-    if (slices != 0 && slices != 4 && slices != 8) return RV_ERR_BAD_SIZE;
-    if (slices == 4 && N > 256) return RV_ERR_UNSUPPORTED;
-    const bool fine = slices ? slices == 8 : 2LL * ((P + 31) / 32) * heads * n_seqs <= (long long)rv_sm_count();
-#define RV_SCAN_LAUNCH(NPT, NSL)                                                                                                 \
-    RV_LAUNCH_ST = launch_scan<NPT, NSL>(stream, xbc, x_dtype, channels, dt_in, dt_dtype, dt_stride, dt_col0, dt_bias, a_log,    \
-                                         d_skip, p_dtype, cu_seqlens, state_slots, state, (size_t)state_stride, y, n_seqs, heads, P, N, groups)
-    if (fine) {
-        if (N <= 32) RV_SCAN_LAUNCH(4, 8);
-        else if (N <= 64) RV_SCAN_LAUNCH(8, 8);
-        else if (N <= 128) RV_SCAN_LAUNCH(16, 8);
-        else RV_SCAN_LAUNCH(32, 8);
+    // one column per thread (16 per block) only where blocks of 32 columns would leave half of the SMs without one, and for
+    // the largest states (two columns of 32 state values each would not fit the registers)
+    const bool narrow = columns ? columns == 1 : (N > 128 || 2LL * ((P + 31) / 32) * heads * n_seqs <= (long long)rv_sm_count());
+#define RV_SCAN_LAUNCH(NPT, NC)                                                                                                  \
+    RV_LAUNCH_ST = launch_scan<NPT, NC>(stream, xbc, x_dtype, channels, dt_in, dt_dtype, dt_stride, dt_col0, dt_bias, a_log,     \
+                                        d_skip, p_dtype, cu_seqlens, state_slots, state, (size_t)state_stride, y, n_seqs, heads, P, N, groups)
+    if (narrow || N > 128) {
+        if (N <= 32) RV_SCAN_LAUNCH(4, 1);
+        else if (N <= 64) RV_SCAN_LAUNCH(8, 1);
+        else if (N <= 128) RV_SCAN_LAUNCH(16, 1);
+        else RV_SCAN_LAUNCH(32, 1);
     } else {
-        if (N <= 16) RV_SCAN_LAUNCH(4, 4);
-        else if (N <= 32) RV_SCAN_LAUNCH(8, 4);
-        else if (N <= 64) RV_SCAN_LAUNCH(16, 4);
-        else if (N <= 128) RV_SCAN_LAUNCH(32, 4);
-        else RV_SCAN_LAUNCH(64, 4);
+        if (N <= 32) RV_SCAN_LAUNCH(4, 2);
+        else if (N <= 64) RV_SCAN_LAUNCH(8, 2);
+        else RV_SCAN_LAUNCH(16, 2);
     }
 #undef RV_SCAN_LAUNCH
     return rv_launch_status();

@@ -924,11 +924,11 @@ class CudaKernels:
         return out
 
     def ssm_scan(self, xbc, proj, dt_col0: int, dt_bias, a_log, d_skip, cu_seqlens, state_slots, state, heads: int,
-                 head_dim: int, state_size: int, groups: int, slices: int = 0) -> torch.Tensor:
+                 head_dim: int, state_size: int, groups: int, columns: int = 0) -> torch.Tensor:
         """The selective-state recurrence over the step's tokens, continued from and leaving behind each request's
         S in `state` (float [slots, floats], [heads][N][P] at offset 0).  xbc rows: [x | B | C]; raw dt is read
-        from columns dt_col0 .. of `proj`.  Returns y float32 [T, heads * head_dim].  `slices`: into how many parts
-        (4 or 8) a block cuts the state dimension; 0 lets the launcher choose by the size of the grid."""
+        from columns dt_col0 .. of `proj`.  Returns y float32 [T, heads * head_dim].  `columns`: columns of the
+        state per thread (1 or 2); 0 lets the launcher choose by the size of the grid."""
         _need(xbc, "xbc", dims=2); _need(proj, "proj", dims=2); _need(state, "state", torch.float32, 2)
         for name, p in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
             _need(p, name, dt_bias.dtype, 1)
@@ -941,7 +941,7 @@ class CudaKernels:
             _ptr(xbc), c_int(self._dt(xbc, "xbc")), c_int(xbc.shape[1]), _ptr(proj), c_int(self._dt(proj, "proj")),
             c_int(proj.shape[1]), c_int(dt_col0), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), c_int(self._dt(dt_bias, "dt_bias")),
             _ptr(cu_seqlens), _ptr(state_slots), _ptr(state), ctypes.c_longlong(state.shape[1]), _ptr(y),
-            c_int(state_slots.shape[0]), c_int(heads), c_int(head_dim), c_int(state_size), c_int(groups), c_int(slices),
+            c_int(state_slots.shape[0]), c_int(heads), c_int(head_dim), c_int(state_size), c_int(groups), c_int(columns),
             self._stream())
         _check("ssm_scan", st)
         return y

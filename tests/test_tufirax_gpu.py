@@ -233,9 +233,11 @@ def test_causal_conv_through_state(K, dtype, taps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("slices", [4, 8])
+@pytest.mark.parametrize("columns", [1, 2])
 @pytest.mark.parametrize("heads,Pd,N,groups", [(6, 20, 24, 3), (4, 33, 40, 1), (8, 64, 128, 2), (2, 48, 7, 2), (3, 16, 200, 1)])
-def test_scan_through_state(K, dtype, heads, Pd, N, groups, slices):
+def test_scan_through_state(K, dtype, heads, Pd, N, groups, columns):
+    if columns == 2 and N > 128:
+        pytest.skip("states beyond 128 values keep one column per thread")
     lens, slots = [37, 3, 18], [1, 3, 0]
     inner, ch = heads * Pd, heads * Pd + 2 * groups * N
     xbc = [rnd(n, ch, seed=50 + i).to(dtype) for i, n in enumerate(lens)]
@@ -260,7 +262,7 @@ def test_scan_through_state(K, dtype, heads, Pd, N, groups, slices):
         rows.append(torch.ones(1, ch, dtype=dtype)); drows.append(torch.zeros(1, heads)); cu.append(cu[-1] + 1); sl.append(-1)
         proj = torch.cat([torch.zeros(cu[-1], 3), torch.cat(drows)], 1).cuda()
         y = K.ssm_scan(torch.cat(rows).cuda(), proj, 3, dt_bias.cuda(), a_log.cuda(), D.cuda(), torch.tensor(cu, dtype=torch.int32).cuda(),
-                       torch.tensor(sl, dtype=torch.int32).cuda(), state, heads, Pd, N, groups, slices=slices)
+                       torch.tensor(sl, dtype=torch.int32).cuda(), state, heads, Pd, N, groups, columns=columns)
         assert y.dtype == torch.float32 and float(y[-1].abs().max()) == 0           # the padding row
         r = 0
         for s, n in enumerate(cut):
