@@ -498,6 +498,20 @@ def run_tufirax(args):
     # attention: one prompt of 2,048 tokens, and a decode step of `batch` sequences behind 2,048 tokens
     nh, nkv, hd = z["heads"], z["kv_heads"], z["dim"]
     sinks = torch.zeros(nh, device=dev)
+    # what follows the q/k(/v) product: norms over the whole rows, rotation, cache write, gate - beside bias-free rotation and cache write
+    pages = PROMPT // 16
+    cache1 = torch.zeros(pages, 2, nkv, 16, hd, dtype=bf, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * torch.tensor([500000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64)[None, :]
+    cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+    proj_qkg = torch.randn(T, (nh + nkv) * hd + nh, device=dev)
+    proj_qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=dev)
+    wq, wk = torch.ones(nh * hd, dtype=bf, device=dev), torch.ones(nkv * hd, dtype=bf, device=dev)
+    ms_like = _time_kernel(lambda: K.rope_cache_write(proj_qkv, None, pos, cos, sin, pos, cache1, nh, nkv, hd, out_dtype=bf), flush=flush)
+    like = {"kernel": "rope_cache_write", "ms": round(ms_like, 4), "frac_hbm": round(T * (nh + 2 * nkv) * hd * 6 / (ms_like / 1e3) / bw, 3)}
+    row("qk_norm_rope_cache_write", _time_kernel(lambda: K.qk_norm_rope_cache_write(proj_qkg, wq, wk, 1e-6, pos, cos, sin, pos, cache1, nh, nkv, hd,
+                                                                                    bf, with_gate=True), flush=flush),
+        T * ((nh + nkv) * hd * 6 + nkv * hd * 2 + nh * 8), like)
 
     def attention_case(q_len, ctx, seqs):
         pages = seqs * (ctx // 16)
