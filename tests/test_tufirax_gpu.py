@@ -325,6 +325,30 @@ def test_replay_matches_plain(tmp_path, which, schedule, dtype):
         TT.compare(got, ref, 8e-2, what)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_odd_shapes_whole_and_mixed(tmp_path, dtype):
+    """Sizes off every fast path (see tufirax_tools.odd_shapes), whole prompts and the mixed schedule."""
+    from rvllm_b200 import load_config
+    from rvllm_b200.engine import trace as trace_mod
+    folder = X.write_folder(X.odd_shapes(), seed=8, edit=X.lively)
+    vocab = load_config(folder).vocab_size
+    reqs = random_requests(vocab, (70, 150, 9, 33, 130), seed=6)
+    ref = X.plain_logits(folder, reqs)
+    rounded = X.plain_logits(folder, reqs, rounded=True) if dtype == "bfloat16" else None
+    for name, make in (("whole", TT.schedule_whole), ("mixed", TT.schedule_mixed)):
+        out = tmp_path / name
+        trace = make(reqs)
+        engine = trace_mod.build_engine(folder, dtype, trace.max_tokens, 16)
+        trace_mod.replay(engine, io.StringIO(trace.lines()), str(out), io.StringIO())
+        engine.cache.check()
+        got = TT.read_logits(str(out), trace, vocab)
+        if dtype == "float32":
+            TT.compare(got, ref, 1e-4, f"odd/{name}")
+        else:
+            TT.compare_bfloat16(got, ref, rounded, f"odd/{name}")
+        del engine
+
+
 def test_generation_through_the_entry_point():
     """Greedy tokens through LLM.generate and its scheduler (decode steps from CUDA graphs, prompts in portions,
     more requests than slots): float32 equals the plain implementation token for token; bfloat16 may differ only

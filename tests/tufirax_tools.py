@@ -56,6 +56,17 @@ def small_b() -> dict:
                    shared(a, 0)], width=96, vocab=300, eps=1e-6)
 
 
+def odd_shapes() -> dict:
+    """Sizes that no kernel's fast path is made for: a width and a vocabulary that are no multiples of 8, head sizes
+    40 (no tensor-core attention kernel) and 96, a state of 13 and one of 256, two and eight taps, as many groups as
+    heads, a norm group per head, a feed-forward narrower than the model."""
+    return config([mamba2(heads=3, vdim=24, state=13, groups=3, conv=2, norm_groups=3, ff=36),
+                   attention(heads=4, kv_heads=4, dim=40, rot_dims=40, base=77.0, scale=0.2, softcap=4.0, ff=None),
+                   mamba2(heads=2, vdim=8, state=256, groups=1, conv=8, norm_groups=2, ff=None),
+                   attention(heads=6, kv_heads=3, dim=96, rot_dims=32, base=1e6, scale=0.09, softcap=50.0, ff=52)],
+                  width=76, vocab=173, eps=1e-5)
+
+
 def write_folder(cfg: dict, seed: int = 0, dtype: str = "bfloat16", edit=None) -> str:
     """A model folder written by the framework's random-weights mode; `edit(tensors)` may change the
     tensors (a dictionary name -> tensor) before they are written."""
