@@ -184,7 +184,8 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
                 const void* __restrict__ dt_bias, const void* __restrict__ a_log, const void* __restrict__ d_skip, int p_dtype,
                 const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
                 float* __restrict__ state, size_t state_stride, float* __restrict__ y,
-                int heads, int P, int N, int groups) {
+                int heads, int P, int N, int groups,
+                int seg_tokens, int max_segs, float* __restrict__ seg_state, float* __restrict__ seg_decay, float* __restrict__ dcum) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     constexpr int NSL = 8;                            // slices of the state dimension
@@ -200,8 +201,17 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
     float* sDec = sY + RV_SCAN_CHUNK * COLS;  // [chunk]       exp(-exp(A_log) dt)
     float* sDt = sDec + RV_SCAN_CHUNK;                // [chunk]
     const int tid = threadIdx.x;
-    const int seq = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * COLS;
-    const int start = cu_seqlens[seq], n_tok = cu_seqlens[seq + 1] - start;
+    // With seg_tokens > 0 a sequence's tokens are cut into segments of that many and grid.z counts (sequence, segment):
+    // segment 0 starts from the request's state, the others from zero; a sequence of several segments leaves each
+    // segment's last state, the product of its decays and the running product at every token in scratch memory, from which
+    // ssm_segment_carry_kernel and ssm_segment_correct_kernel put the pieces together.
+    const int seq = blockIdx.z / max_segs, seg = blockIdx.z - seq * max_segs;
+    const int h = blockIdx.y, p0 = blockIdx.x * COLS;
+    const int seq_start = cu_seqlens[seq], seq_tok = cu_seqlens[seq + 1] - seq_start;
+    const int n_segs = seg_tokens > 0 ? (seq_tok + seg_tokens - 1) / seg_tokens : 1;
+    if (seg >= n_segs) return;
+    const int start = seq_start + seg * seg_tokens;
+    const int n_tok = seg_tokens > 0 ? (seq_tok - seg * seg_tokens < seg_tokens ? seq_tok - seg * seg_tokens : seg_tokens) : seq_tok;
     const int slot = state_slots[seq];
     const int inner = heads * P;
     const int lane_p = (tid / NSL) * NC, slice = tid % NSL;      // the thread's first column within the block
@@ -224,7 +234,7 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
 #pragma unroll
         for (int i = 0; i < NPT; ++i) {
             const int n = slice * NPT + i;
-            s[c][i] = (p + c < P && n < N) ? S[(size_t)n * P + p + c] : 0.f;
+            s[c][i] = (seg == 0 && p + c < P && n < N) ? S[(size_t)n * P + p + c] : 0.f;
         }
     for (int i = tid; i < 2 * RV_SCAN_CHUNK * TOK; i += blockDim.x) sm[i] = 0.f;      // state indices beyond N stay zero
     const size_t b_col = (size_t)inner + (size_t)g * N, c_col = (size_t)inner + (size_t)groups * N + (size_t)g * N;
@@ -307,6 +317,8 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
         }
     };
 
+    float run = 1.f;                                   // product of the decays from the segment's first token on
+    const bool keeps_run = n_segs > 1 && tid == 0 && blockIdx.x == 0;
     if (vec && n_tok > 0) fetch(0);
     for (int t0 = 0; t0 < n_tok; t0 += RV_SCAN_CHUNK) {
         const int nt = n_tok - t0 < RV_SCAN_CHUNK ? n_tok - t0 : RV_SCAN_CHUNK;
@@ -316,6 +328,8 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
         if (vec && t0 + RV_SCAN_CHUNK < n_tok) fetch(t0 + RV_SCAN_CHUNK);
         auto token = [&](int tk) {
             const float dec = sDec[tk], dtv = sDt[tk];
+            run *= dec;
+            if (keeps_run) dcum[(size_t)(start + t0 + tk) * heads + h] = run;
             const float4* B4 = reinterpret_cast<const float4*>(sB + tk * TOK + slice * SEG);
             const float4* C4 = reinterpret_cast<const float4*>(sC + tk * TOK + slice * SEG);
             float xv[NC], dx[NC], acc[NC][4];
@@ -357,47 +371,146 @@ ssm_scan_kernel(const void* __restrict__ xbc, int x_dtype, int channels,        
             if (pp < P) y[(size_t)(start + t0 + tk) * inner + h * P + pp] = sY[i];
         }
     }
+    float* S_out = n_segs == 1 ? S : seg_state + ((size_t)blockIdx.z * heads + h) * N * P;
 #pragma unroll
     for (int c = 0; c < NC; ++c)
 #pragma unroll
         for (int i = 0; i < NPT; ++i) {
             const int n = slice * NPT + i;
-            if (p + c < P && n < N) S[(size_t)n * P + p + c] = s[c][i];
+            if (p + c < P && n < N) S_out[(size_t)n * P + p + c] = s[c][i];
         }
+    if (keeps_run) seg_decay[(size_t)blockIdx.z * heads + h] = run;
+}
+
+// A sequence of several segments: element by element, the state walks through the segments,
+//     S_start(1) = what segment 0 left (it started from the request's state),  S_start(k + 1) = decay(k) S_start(k) + S_local(k),
+// every S_local(k), k >= 1, in scratch is replaced by S_start(k), and the last value becomes the request's state.
+__global__ void __launch_bounds__(256)
+ssm_segment_carry_kernel(const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, float* __restrict__ state,
+                         size_t state_stride, float* __restrict__ seg_state, const float* __restrict__ seg_decay, int heads,
+                         int NP, int seg_tokens, int max_segs) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int h = blockIdx.y, seq = blockIdx.z;
+    if (e >= NP) return;
+    const int n_segs = (cu_seqlens[seq + 1] - cu_seqlens[seq] + seg_tokens - 1) / seg_tokens;
+    const int slot = state_slots[seq];
+    if (n_segs <= 1 || slot < 0) return;
+    float* sp = state + (size_t)slot * state_stride + (size_t)h * NP + e;
+    // segment 0 started from the request's state, so what it left is already the state at the start of segment 1
+    float S = seg_state[(((size_t)seq * max_segs) * heads + h) * NP + e];
+    for (int k = 1; k < n_segs; ++k) {
+        const size_t idx = ((size_t)seq * max_segs + k) * heads + h;
+        const float local = seg_state[idx * NP + e];
+        seg_state[idx * NP + e] = S;
+        S = fmaf(seg_decay[idx], S, local);
+    }
+    *sp = S;
+}
+
+// What the state at a segment's start adds to the outputs of its tokens (segments 1 and later; the scan ran them from zero):
+//     y_t += (product of the decays from the segment's first token to t) * S_start^T C_t.
+// Grid (P / 32, heads, sequences x segments); 128 threads = 32 columns x 4 groups of 4 tokens of a chunk of 16.
+__global__ void __launch_bounds__(128)
+ssm_segment_correct_kernel(const void* __restrict__ xbc, int x_dtype, int channels, const int* __restrict__ cu_seqlens,
+                           const int* __restrict__ state_slots, const float* __restrict__ seg_state,
+                           const float* __restrict__ dcum, float* __restrict__ y, int heads, int P, int N, int groups,
+                           int seg_tokens, int max_segs) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    float* sS = sm;                  // [N][32]  S_start of this head's 32 columns
+    float* sCt = sm + N * 32;        // [N][16]  C of a chunk's tokens, transposed
+    const int seq = blockIdx.z / max_segs, seg = blockIdx.z - seq * max_segs;
+    const int h = blockIdx.y, p0 = blockIdx.x * 32;
+    const int seq_start = cu_seqlens[seq], seq_tok = cu_seqlens[seq + 1] - seq_start;
+    const int n_segs = (seq_tok + seg_tokens - 1) / seg_tokens;
+    if (seg == 0 || seg >= n_segs || state_slots[seq] < 0) return;
+    const int start = seq_start + seg * seg_tokens;
+    const int n_tok = seq_tok - seg * seg_tokens < seg_tokens ? seq_tok - seg * seg_tokens : seg_tokens;
+    const int inner = heads * P, g = h / (heads / groups);
+    const size_t c_col = (size_t)inner + (size_t)groups * N + (size_t)g * N;
+    const float* S0 = seg_state + ((size_t)blockIdx.z * heads + h) * N * P;
+    const int tid = threadIdx.x, pl = tid & 31, tq = tid >> 5;
+    for (int i = tid; i < N * 32; i += 128) {
+        const int n = i >> 5, pp = p0 + (i & 31);
+        sS[i] = pp < P ? S0[(size_t)n * P + pp] : 0.f;
+    }
+    for (int t0 = 0; t0 < n_tok; t0 += 16) {
+        const int nt = n_tok - t0 < 16 ? n_tok - t0 : 16;
+        __syncthreads();
+#pragma unroll 4
+        for (int i = tid; i < 16 * N; i += 128) {
+            const int tk = i / N, n = i - tk * N;
+            sCt[n * 16 + tk] = tk < nt ? rv_load_any(xbc, x_dtype, (size_t)(start + t0 + tk) * channels + c_col + n) : 0.f;
+        }
+        __syncthreads();
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 8
+        for (int n = 0; n < N; ++n) {
+            const float sv = sS[n * 32 + pl];
+            const float4 c = *reinterpret_cast<const float4*>(sCt + n * 16 + tq * 4);
+            a0 = fmaf(sv, c.x, a0); a1 = fmaf(sv, c.y, a1); a2 = fmaf(sv, c.z, a2); a3 = fmaf(sv, c.w, a3);
+        }
+        const float acc[4] = {a0, a1, a2, a3};
+        if (p0 + pl < P)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int tk = tq * 4 + j;
+                if (tk < nt) {
+                    const size_t t = (size_t)(start + t0 + tk);
+                    y[t * inner + h * P + p0 + pl] += dcum[t * heads + h] * acc[j];
+                }
+            }
+    }
 }
 
 template <int NPT, int NC>
 static int launch_scan(cudaStream_t stream, const void* xbc, int x_dtype, int channels, const void* dt_in, int dt_dtype,
                        int dt_stride, int dt_col0, const void* dt_bias, const void* a_log, const void* d_skip, int p_dtype,
                        const int* cu_seqlens, const int* state_slots, float* state, size_t state_stride, float* y, int n_seqs,
-                       int heads, int P, int N, int groups) {
+                       int heads, int P, int N, int groups, int seg_tokens, int max_segs, float* seg_state, float* seg_decay,
+                       float* dcum) {
     constexpr int COLS = NC * 16;
-    const dim3 grid((P + COLS - 1) / COLS, heads, n_seqs);
+    const dim3 grid((P + COLS - 1) / COLS, heads, n_seqs * max_segs);
     const size_t smem = sizeof(float) * ((size_t)2 * RV_SCAN_CHUNK * 8 * (NPT + 4) + 2 * RV_SCAN_CHUNK * COLS + 2 * RV_SCAN_CHUNK);
     static RvPerDevice configured;
     if (smem > 48 * 1024)
         if (int e = rv_configure_smem(configured, ssm_scan_kernel<NPT, NC>, (int)smem)) return e;
     return rv_launch(ssm_scan_kernel<NPT, NC>, grid, dim3(128), smem, stream, xbc, x_dtype, channels, dt_in, dt_dtype, dt_stride, dt_col0,
-                     dt_bias, a_log, d_skip, p_dtype, cu_seqlens, state_slots, state, state_stride, y, heads, P, N, groups);
+                     dt_bias, a_log, d_skip, p_dtype, cu_seqlens, state_slots, state, state_stride, y, heads, P, N, groups,
+                     seg_tokens, max_segs, seg_state, seg_decay, dcum);
 }
 
 // `columns`: columns per thread, 1 or 2; 0 lets the launcher choose by the size of the grid.
+// `seg_tokens` > 0 (a multiple of 16): sequences are cut into segments of that many tokens that run side by side
+// (`max_segs` = the most segments of any sequence; scratch: seg_state [n_seqs * max_segs, heads, N, P], seg_decay
+// [n_seqs * max_segs, heads], dcum [tokens, heads], all float), then two small kernels carry the state through the segments
+// and add what each segment's starting state contributes to its outputs.  The results equal the one-pass walk up to
+// float32 rounding.
 RV_EXPORT int rv_ssm_scan(const void* xbc, int x_dtype, int channels, const void* dt_in, int dt_dtype, int dt_stride, int dt_col0,
                           const void* dt_bias, const void* a_log, const void* d_skip, int p_dtype, const int* cu_seqlens,
                           const int* state_slots, float* state, long long state_stride, float* y, int n_seqs, int heads, int P,
-                          int N, int groups, int columns, cudaStream_t stream) {
+                          int N, int groups, int columns, int seg_tokens, int max_segs, float* seg_state, float* seg_decay,
+                          float* dcum, cudaStream_t stream) {
     if (n_seqs < 0 || heads <= 0 || P <= 0 || N <= 0 || groups <= 0 || heads % groups) return RV_ERR_BAD_SIZE;
     if (channels < heads * P + 2 * groups * N || dt_stride < dt_col0 + heads || dt_col0 < 0) return RV_ERR_BAD_SIZE;
     if ((x_dtype | dt_dtype | p_dtype) & ~1) return RV_ERR_BAD_DTYPE;
     if (columns < 0 || columns > 2) return RV_ERR_BAD_SIZE;
     if (N > 256 || heads > 65535 || n_seqs > 65535) return RV_ERR_UNSUPPORTED;
     if (n_seqs == 0) return RV_OK;
+    if (seg_tokens < 0 || (seg_tokens & 15)) return RV_ERR_BAD_SIZE;
+    if (seg_tokens == 0) max_segs = 1;
+    else if (max_segs < 1 || !seg_state || !seg_decay || !dcum) return RV_ERR_BAD_SIZE;
+    if ((long long)n_seqs * max_segs > 65535) return RV_ERR_UNSUPPORTED;
     // one column per thread (16 per block) only where blocks of 32 columns would leave half of the SMs without one, and for
     // the largest states (two columns of 32 state values each would not fit the registers)
-    const bool narrow = columns ? columns == 1 : (N > 128 || 2LL * ((P + 31) / 32) * heads * n_seqs <= (long long)rv_sm_count());
+    const bool narrow = columns ? columns == 1 : (N > 128 || 2LL * ((P + 31) / 32) * heads * n_seqs * max_segs <= (long long)rv_sm_count());
 #define RV_SCAN_LAUNCH(NPT, NC)                                                                                                  \
     RV_LAUNCH_ST = launch_scan<NPT, NC>(stream, xbc, x_dtype, channels, dt_in, dt_dtype, dt_stride, dt_col0, dt_bias, a_log,     \
-                                        d_skip, p_dtype, cu_seqlens, state_slots, state, (size_t)state_stride, y, n_seqs, heads, P, N, groups)
+                                        d_skip, p_dtype, cu_seqlens, state_slots, state, (size_t)state_stride, y, n_seqs, heads, P, N, groups, \
+                                        seg_tokens, max_segs, seg_state, seg_decay, dcum)
     if (narrow || N > 128) {
         if (N <= 32) RV_SCAN_LAUNCH(4, 1);
         else if (N <= 64) RV_SCAN_LAUNCH(8, 1);
@@ -409,5 +522,13 @@ RV_EXPORT int rv_ssm_scan(const void* xbc, int x_dtype, int channels, const void
         else RV_SCAN_LAUNCH(16, 2);
     }
 #undef RV_SCAN_LAUNCH
+    if (seg_tokens == 0 || max_segs == 1 || RV_LAUNCH_ST != RV_OK) return rv_launch_status();
+    const int NP = N * P;
+    RV_LAUNCH_ST = rv_launch(ssm_segment_carry_kernel, dim3((NP + 255) / 256, heads, n_seqs), dim3(256), 0, stream, cu_seqlens, state_slots,
+                             state, (size_t)state_stride, seg_state, (const float*)seg_decay, heads, NP, seg_tokens, max_segs);
+    if (RV_LAUNCH_ST != RV_OK) return rv_launch_status();
+    RV_LAUNCH_ST = rv_launch(ssm_segment_correct_kernel, dim3((P + 31) / 32, heads, n_seqs * max_segs), dim3(128), (size_t)N * 48 * sizeof(float),
+                             stream, xbc, x_dtype, channels, cu_seqlens, state_slots, (const float*)seg_state, (const float*)dcum, y, heads, P,
+                             N, groups, seg_tokens, max_segs);
     return rv_launch_status();
 }

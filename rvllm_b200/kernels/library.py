@@ -923,12 +923,21 @@ class CudaKernels:
         COUNTERS['launches'] += 1 if taps > 1 else 0
         return out
 
+    SCAN_SEGMENT_TOKENS = 256          # a sequence that brings more than twice as many tokens to a step is scanned in segments
+    SCAN_SEGMENT_SCRATCH = 1 << 30     # ... of this many tokens side by side, while the segments' states fit these bytes of scratch
+    SCAN_SEGMENT_ALWAYS = False        # ... and only where the one-pass walk would have fewer CTAs than the device has SMs (measured:
+                                       # 128 CTAs, 64 heads of 64: the step's prefill 6.4 -> 5.5 ms; 256 CTAs, 128 heads: scan + carry +
+                                       # correction 0.59 + 0.16 + 0.38 ms against 0.92 ms in one pass)
+
     def ssm_scan(self, xbc, proj, dt_col0: int, dt_bias, a_log, d_skip, cu_seqlens, state_slots, state, heads: int,
-                 head_dim: int, state_size: int, groups: int, columns: int = 0) -> torch.Tensor:
+                 head_dim: int, state_size: int, groups: int, columns: int = 0, max_q_len: Optional[int] = None,
+                 segment_tokens: Optional[int] = None) -> torch.Tensor:
         """The selective-state recurrence over the step's tokens, continued from and leaving behind each request's
         S in `state` (float [slots, floats], [heads][N][P] at offset 0).  xbc rows: [x | B | C]; raw dt is read
         from columns dt_col0 .. of `proj`.  Returns y float32 [T, heads * head_dim].  `columns`: columns of the
-        state per thread (1 or 2); 0 lets the launcher choose by the size of the grid."""
+        state per thread (1 or 2); 0 lets the launcher choose by the size of the grid.  `max_q_len`: the most tokens any
+        sequence brings (known on the host); long portions are then cut into segments of `segment_tokens` (default
+        `SCAN_SEGMENT_TOKENS`) that are scanned side by side and joined by two small kernels."""
         _need(xbc, "xbc", dims=2); _need(proj, "proj", dims=2); _need(state, "state", torch.float32, 2)
         for name, p in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
             _need(p, name, dt_bias.dtype, 1)
@@ -937,13 +946,27 @@ class CudaKernels:
         if state.shape[1] < heads * state_size * head_dim:
             raise KernelError("ssm_scan: the state rows are too short")
         y = torch.empty((xbc.shape[0], heads * head_dim), dtype=torch.float32, device=xbc.device)
+        seg = self.SCAN_SEGMENT_TOKENS if segment_tokens is None else segment_tokens
+        n_seqs, max_segs, seg_state, seg_decay, dcum = state_slots.shape[0], 1, None, None, None
+        few_ctas = self.SCAN_SEGMENT_ALWAYS or segment_tokens is not None or -(-head_dim // 32) * heads * n_seqs < self.num_sms
+        if seg and few_ctas and max_q_len is not None and max_q_len > 2 * seg:
+            max_segs = -(-max_q_len // seg)
+            if n_seqs * max_segs * heads * state_size * head_dim * 4 <= self.SCAN_SEGMENT_SCRATCH and n_seqs * max_segs <= 65535:
+                seg_state = torch.empty((n_seqs * max_segs, heads, state_size, head_dim), dtype=torch.float32, device=xbc.device)
+                seg_decay = torch.empty((n_seqs * max_segs, heads), dtype=torch.float32, device=xbc.device)
+                dcum = torch.empty((xbc.shape[0], heads), dtype=torch.float32, device=xbc.device)
+            else:
+                max_segs = 1
+        if seg_state is None:
+            seg = 0
         st = self._lib("ssm.cu").rv_ssm_scan(
             _ptr(xbc), c_int(self._dt(xbc, "xbc")), c_int(xbc.shape[1]), _ptr(proj), c_int(self._dt(proj, "proj")),
             c_int(proj.shape[1]), c_int(dt_col0), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), c_int(self._dt(dt_bias, "dt_bias")),
             _ptr(cu_seqlens), _ptr(state_slots), _ptr(state), ctypes.c_longlong(state.shape[1]), _ptr(y),
             c_int(state_slots.shape[0]), c_int(heads), c_int(head_dim), c_int(state_size), c_int(groups), c_int(columns),
-            self._stream())
+            c_int(seg), c_int(max_segs), _ptr(seg_state), _ptr(seg_decay), _ptr(dcum), self._stream())
         _check("ssm_scan", st)
+        COUNTERS['launches'] += 2 if seg else 0
         return y
 
     def gated_group_rmsnorm(self, y, proj, gamma, eps: float, parts: int, out_dtype) -> torch.Tensor:

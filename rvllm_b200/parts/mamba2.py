@@ -66,7 +66,7 @@ class Mamba2Mixer(Part):
         xbc = k.causal_conv_silu(proj, self.inner, self.channels, self.conv_w, self.conv_b, ctx.token_seq, ctx.cu_seqlens,
                                  ctx.state_slots, cache.state, self.ssm_floats, x.dtype)
         y = k.ssm_scan(xbc, proj, self.inner + self.channels, self.dt_bias, self.a_log, self.d_skip, ctx.cu_seqlens,
-                       ctx.state_slots, cache.state, self.heads, self.head_dim, self.state, self.groups)
+                       ctx.state_slots, cache.state, self.heads, self.head_dim, self.state, self.groups, max_q_len=max(ctx.q_lens))
         y = k.gated_group_rmsnorm(y, proj, self.norm, self.eps, self.norm_groups, x.dtype)
         return self.out(y, ctx, residual=residual, out_dtype=out_dtype)
 

@@ -83,7 +83,7 @@ class EmulatedKernels:
         return out.to(out_dtype)
 
     def ssm_scan(self, xbc, proj, dt_col0, dt_bias, a_log, d_skip, cu_seqlens, state_slots, state, heads, head_dim,
-                 state_size, groups):
+                 state_size, groups, columns=0, max_q_len=None, segment_tokens=None):
         T = xbc.shape[0]
         inner, P, N = heads * head_dim, head_dim, state_size
         xf = xbc.float()

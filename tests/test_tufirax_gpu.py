@@ -274,6 +274,49 @@ def test_scan_through_state(K, dtype, heads, Pd, N, groups, columns):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,Pd,N,groups,seg", [(6, 20, 24, 3, 16), (4, 33, 40, 1, 32), (8, 64, 128, 2, 48), (2, 16, 256, 1, 16)])
+def test_scan_in_segments(K, dtype, heads, Pd, N, groups, seg):
+    """Long portions cut into segments that are scanned side by side and joined: the same outputs and the same final
+    state as the plain recurrence, continued from a state that an earlier step left, beside a short sequence (one
+    segment), a sequence of exactly two segments and a padding row; slow and fast decays."""
+    lens, slots = [5 * seg + 7, 3, 2 * seg, 1], [2, 0, 3, -1]
+    first = [9, 2, 0, 0]                                   # tokens that an earlier, unsegmented step brings
+    inner, ch = heads * Pd, heads * Pd + 2 * groups * N
+    xbc = [rnd(f + n, ch, seed=150 + i).to(dtype) for i, (f, n) in enumerate(zip(first, lens))]
+    dtr = [rnd(f + n, heads, seed=160 + i, scale=2.0).float() for i, (f, n) in enumerate(zip(first, lens))]
+    dt_bias, D = rnd(heads, seed=170).float(), rnd(heads, seed=172).float()
+    a_log = torch.linspace(-5.0, 1.0, heads)
+    want = []
+    for u, d in zip(xbc, dtr):
+        n, ud = u.shape[0], u.double()
+        want.append(P.selective_scan(ud[:, :inner].reshape(n, heads, Pd), ud[:, inner:inner + groups * N].reshape(n, groups, N),
+                                     ud[:, inner + groups * N:].reshape(n, groups, N), P.softplus(d.double() + dt_bias.double()),
+                                     a_log.double(), D.double(), groups).reshape(n, inner))
+    state = torch.zeros((4, heads * N * Pd + 2), dtype=torch.float32, device="cuda")
+    state[1] = 3.0
+    ref_state = state.clone()
+    for use_segments, st in ((True, state), (False, ref_state)):
+        for step, counts in enumerate((first, lens)):
+            rows, drows, cu, sl, at = [], [], [0], [], []
+            for s, n in enumerate(counts):
+                if n:
+                    a = 0 if step == 0 else first[s]
+                    rows.append(xbc[s][a:a + n]); drows.append(dtr[s][a:a + n]); cu.append(cu[-1] + n); sl.append(slots[s]); at.append((s, a, n))
+            proj = torch.cat(drows).cuda()
+            y = K.ssm_scan(torch.cat(rows).cuda(), proj, 0, dt_bias.cuda(), a_log.cuda(), D.cuda(), torch.tensor(cu, dtype=torch.int32).cuda(),
+                           torch.tensor(sl, dtype=torch.int32).cuda(), st, heads, Pd, N, groups,
+                           max_q_len=max(counts) if use_segments else None, segment_tokens=seg)
+            r = 0
+            for s, a, n in at:
+                if slots[s] >= 0:
+                    assert rel_err(y[r:r + n], want[s][a:a + n]) < 2e-5, (use_segments, step, s)
+                else:
+                    assert float(y[r:r + n].abs().max()) == 0
+                r += n
+    assert rel_err(state[:, :heads * N * Pd], ref_state[:, :heads * N * Pd]) < 2e-5 and float((state[1] - 3.0).abs().max()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("width,parts", [(120, 4), (132, 1), (2048, 2)])
 def test_gated_group_norm(K, dtype, width, parts):
     y, z, g = rnd(6, width, seed=80, scale=2.0).float(), rnd(6, width + 9, seed=81).float(), (rnd(width, seed=82) + 1).to(dtype)
@@ -283,7 +326,7 @@ def test_gated_group_norm(K, dtype, width, parts):
 
 
 # ---------------------------------------------------------------------------------------- the whole path
-LENGTHS = {"a": (45, 170, 33, 81, 1, 138), "b": (90, 37, 310, 64, 151, 2)}
+LENGTHS = {"a": (45, 170, 33, 81, 1, 138), "b": (90, 37, 700, 64, 151, 2)}      # 700: beyond two segments of the scan
 SCHEDULES = {"whole": TT.schedule_whole, "bulk_tail": TT.schedule_bulk_tail, "portions": TT.schedule_portions,
              "mixed": TT.schedule_mixed}
 _cache = {}
@@ -320,9 +363,9 @@ def test_replay_matches_plain(tmp_path, which, schedule, dtype):
         TT.compare(got, ref, 1e-4, what)
     else:
         # against what storing activations in bfloat16 costs by itself on the same requests (no position beyond
-        # 1.5 x its worst, the median within 1.25 x its median), and no position beyond a plain bound either
+        # 1.5 x its worst, the median within 1.25 x its median), and no position beyond a loose plain bound either
         TT.compare_bfloat16(got, ref, _cache[which][4], what)
-        TT.compare(got, ref, 8e-2, what)
+        TT.compare(got, ref, 0.2, what)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
