@@ -37,7 +37,7 @@ def test_residual_rmsnorm(K, dtype, cols):
     want = r + P.rms(y.float().double(), 1e-5) * g.to(dtype).double()
     res = r.float().cuda()
     out, rounded = K.residual_rmsnorm(y.float().cuda(), g.to(dtype).cuda(), 1e-5, res, dtype)
-    assert out is res and rel_err(out, want.float().double() if False else want) < 2e-6
+    assert out is res and rel_err(out, want) < 2e-6            # the stream is updated in place
     assert rounded.dtype == dtype and rel_err(rounded, want) < (2e-6 if dtype == torch.float32 else 5e-3)
     # without a stream: a plain norm of a float32 row into the activations' type
     n = K.rmsnorm(y.float().cuda(), g.to(dtype).cuda(), 1e-5, out_dtype=dtype)
@@ -97,7 +97,6 @@ def test_qk_norm_rotation_cache_write(K, dtype, nh, nkv, hd, rot):
             assert rel_err(cache[s // page, 0, :, s % page], kr[0]) < TOL[dtype] / 2, t
             assert rel_err(cache[s // page, 1, :, s % page], pd[t, qw:qw + kw].view(nkv, hd)) < TOL[dtype] / 2, t   # the value: k as projected
     assert rel_err(gate, torch.sigmoid(pd[:, qw + kw:])) < 2e-6
-    assert float(cache[2, :, :, 7 - 0].abs().max()) >= 0            # (slot -1 wrote nothing: checked below)
     untouched = [s for s in range(n_pages * page) if s not in set(slots.tolist())]
     assert all(float(cache[s // page, :, :, s % page].abs().max()) == 0 for s in untouched)
 
@@ -192,11 +191,6 @@ def test_decode_only_step_with_splits(K):
 
 
 # ---------------------------------------------------------------------------------------- state-space mixer
-def _steps(cuts):
-    """cuts: per step, the number of tokens of each of the sequences (0: absent) -> (token_seq, cu_seqlens, slots rows)."""
-    return cuts
-
-
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("taps", [1, 3, 4, 6])
 def test_causal_conv_through_state(K, dtype, taps):
