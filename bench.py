@@ -579,7 +579,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES), help="layer sizes of the model")
     ap.add_argument("--workload", default="decode", choices=["decode", "serve", "tufirax"],
-                    help="decode: the contract's line; serve: continuous batching of uneven prompts; tufirax: the Tufirax "
+                    help="decode: the benchmark's one JSON line; serve: continuous batching of uneven prompts; tufirax: the Tufirax "
                          "design at real layer sizes beside the Llama decoder of equal size, and its kernels alone")
     ap.add_argument("--sizes", default="", help="tufirax: which sizes to run, with commas (default: all)")
     ap.add_argument("--requests", type=int, default=64, help="serve: number of requests")

@@ -155,7 +155,10 @@ def test_models_of_one_kind_of_layer(emulated, kind):
     """Only state (no page group at all) or only pages (no state): the engine asks for nothing it does not need."""
     from rvllm_b200.engine.step import StepEntry
     layer = X.mamba2(ff=40) if kind == "mamba2" else X.attention(heads=2, kv_heads=1, dim=16, rot_dims=8)
-    folder = X.write_folder(X.config([layer, X.shared(layer, 0)], width=48, vocab=97), seed=2, edit=X.lively)
+    # (the borrowing layer comes FIRST in the mamba2 model: a layer may name a later one)
+    layers = [X.shared(layer, 1), layer] if kind == "mamba2" else [layer, X.shared(layer, 0)]
+    folder = X.write_folder(X.config(layers, width=48, vocab=97), seed=2, edit=X.lively)
+    assert set(n.split(".")[0] for n in X.read_folder(folder)[1] if n.startswith("l")) == ({"l1"} if kind == "mamba2" else {"l0"})
     toks = random_requests(97, (29,), seed=1)["r0"]
     want = X.plain_logits(folder, {"x": toks})["x"]
     engine = trace_mod.build_engine(folder, "float32", 64, block_size=8, device="cpu")
