@@ -3,7 +3,7 @@ and slots of fixed-size per-request state.
 
 Layers whose mixers need the same thing (same kv heads, head size and window) form a group; a
 group has its own pages, its own block table per request and one device tensor
-[cache slots of the group, num_pages, 2 (k, v), kv_heads, page_size, head_dim].  A page id
+[cache slots of the group, num_pages, planes (2: k, v; 1: one shared row), kv_heads, page_size, head_dim].  A page id
 addresses the same page in every slot of its group.  Pages are handed out when tokens are about
 to be written into them and come back when the request ends, is pre-empted, or - for a window
 group - when every later query is past them.  The block table keeps -1 where a page was
@@ -26,7 +26,7 @@ from .pools import PagePool, SlotPool
 class CacheView:
     """What a mixer sees of its cache slot."""
     group: Optional[int]                 # index of the page group (None: no pages)
-    kv: Optional[torch.Tensor]           # [num_pages, 2, kv_heads, page_size, head_dim]
+    kv: Optional[torch.Tensor]           # [num_pages, planes, kv_heads, page_size, head_dim]
     state: Optional[torch.Tensor] = None  # [max_seqs, *shape]
 
 
@@ -77,7 +77,7 @@ class CacheManager:
         self.requests: Dict[Hashable, _Request] = {}
         if allocate:
             for g in self.groups:
-                g.tensor = torch.zeros((len(g.cache_slots), num_pages, 2, g.need.num_kv_heads, page_size,
+                g.tensor = torch.zeros((len(g.cache_slots), num_pages, g.need.planes, g.need.num_kv_heads, page_size,
                                         g.need.head_dim), dtype=dtype, device=device)
             for slot, need in self._state_needs.items():
                 self._state[slot] = torch.zeros((max_seqs, *need.shape), dtype=getattr(torch, need.dtype), device=device)
@@ -87,7 +87,7 @@ class CacheManager:
     def bytes_per_page(needs: Dict[int, object], page_size: int, dtype: torch.dtype) -> int:
         """Bytes that one more page per group costs over all cache slots."""
         el = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * n.num_kv_heads * page_size * n.head_dim * el for n in needs.values() if isinstance(n, KvCacheNeed))
+        return sum(n.planes * n.num_kv_heads * page_size * n.head_dim * el for n in needs.values() if isinstance(n, KvCacheNeed))
 
     @staticmethod
     def state_bytes_per_request(needs: Dict[int, object]) -> int:

@@ -11,6 +11,7 @@ from typing import Any, Dict, Type
 from ..errors import ConfigError
 from .model_config import LlamaConfig, Qwen2Config, read_config_json
 from .tufirax_config import TufiraxConfig
+from .vipelix_config import VipelixConfig
 
 _ARCHITECTURES: Dict[str, Type] = {}
 
@@ -53,3 +54,4 @@ def load_config(model_dir: str):
 register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("Qwen2ForCausalLM", Qwen2Config)
 register_architecture("Tufirax", TufiraxConfig)
+register_architecture("Vipelix", VipelixConfig)

@@ -66,11 +66,14 @@ class RunEntry:
     `layer` indexes `ModelSpec.layers` (a layer may appear more than once);
     `cache` is the cache slot the mixer uses: entries with the same number share keys
     and values (or state); `writes_cache` is False for an entry that only reads what
-    another entry wrote.
+    another entry wrote.  `before` names hooks (registry HOOKS, `__call__(x, ctx) -> x`) that act on
+    the residual stream right before the entry's layer runs: what a model adds at the start of a pass
+    over a run of layers that it repeats, for instance.
     """
     layer: int
     cache: int
     writes_cache: bool = True
+    before: Tuple[PartSpec, ...] = ()
 
 
 @dataclass(frozen=True)

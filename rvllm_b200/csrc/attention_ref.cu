@@ -13,18 +13,20 @@
 // denominator - a key without a value, neither scaled nor capped; `gate` (float [tokens, heads])
 // multiplies each head's output.
 //
-// Cache layer layout: [num_pages, 2 (k, v), nkv, page_size, hd].
+// Cache layer layout: [num_pages, planes, nkv, page_size, hd].  planes = 2: keys in plane 0, values in plane 1.
+// planes = 1: one row per token and kv head; the key is the whole row and the value its leading `vd` elements
+// (a latent that keys and values are projections of).  The output row of a head has `vd` elements (hd with two planes).
 #include "common.cuh"
 
-#define MAX_DIMS_PER_LANE 8   // head_dim <= 256
-
-template <typename T>
+// MAX_DIMS_PER_LANE: elements of a row that one lane holds (row <= 32 * MAX_DIMS_PER_LANE; the launcher picks 8 or 32)
+template <typename T, int MAX_DIMS_PER_LANE>
 __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
                                            const int* __restrict__ block_tables, const int* __restrict__ cu_seqlens,
                                            const int* __restrict__ ctx_lens, const int* __restrict__ token_seq,
                                            T* __restrict__ out, int n_tokens, int nh, int nkv, int hd,
                                            int page_size, int max_blocks, float scale, int window,
-                                           float softcap, const float* __restrict__ sinks, const float* __restrict__ gate) {
+                                           float softcap, const float* __restrict__ sinks, const float* __restrict__ gate,
+                                           int planes, int vd) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -33,10 +35,10 @@ __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __r
     const int h = blockIdx.y * (blockDim.x >> 5) + warp;
     if (h >= nh || t >= n_tokens) return;
     const int seq = token_seq[t];
-    T* o = out + ((size_t)t * nh + h) * hd;
+    T* o = out + ((size_t)t * nh + h) * vd;
     const int ctx = seq >= 0 ? ctx_lens[seq] : 0;
     if (ctx <= 0) {
-        for (int d = lane; d < hd; d += 32) o[d] = rv_from_float<T>(0.f);
+        for (int d = lane; d < vd; d += 32) o[d] = rv_from_float<T>(0.f);
         return;
     }
     const int q_start = cu_seqlens[seq];
@@ -55,8 +57,8 @@ __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __r
     }
     float m = -INFINITY, l = 0.f;
     const int* table = block_tables + (size_t)seq * max_blocks;
-    const size_t page_stride = (size_t)2 * nkv * page_size * hd;
-    const size_t v_off = (size_t)nkv * page_size * hd;
+    const size_t page_stride = (size_t)planes * nkv * page_size * hd;
+    const size_t v_off = planes == 2 ? (size_t)nkv * page_size * hd : 0;
     for (int j = lo; j <= pos; ++j) {
         const int page = table[j / page_size];
         const T* kp = cache + (size_t)page * page_stride + ((size_t)kvh * page_size + (j % page_size)) * hd;
@@ -76,7 +78,7 @@ __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __r
 #pragma unroll
         for (int i = 0; i < MAX_DIMS_PER_LANE; ++i) {
             const int d = lane + 32 * i;
-            if (d < hd) acc[i] = acc[i] * corr + p * rv_to_float(vp[d]);
+            if (d < vd) acc[i] = acc[i] * corr + p * rv_to_float(vp[d]);
         }
         m = m_new;
     }
@@ -93,8 +95,45 @@ __global__ void paged_attention_ref_kernel(const T* __restrict__ q, const T* __r
 #pragma unroll
     for (int i = 0; i < MAX_DIMS_PER_LANE; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) o[d] = rv_from_float<T>(acc[i] * inv);
+        if (d < vd) o[d] = rv_from_float<T>(acc[i] * inv);
     }
+}
+
+template <int DPL>
+static int launch_ref(const void* q, const void* cache, const int* block_tables, const int* cu_seqlens, const int* ctx_lens,
+                      const int* token_seq, void* out, int n_tokens, int nh, int nkv, int hd, int page_size, int max_blocks,
+                      float scale, int window, float softcap, const float* sinks, const float* gate, int planes, int vd,
+                      int dtype, cudaStream_t stream) {
+    const int warps = 4;
+    const dim3 grid(n_tokens, (nh + warps - 1) / warps);
+    if (dtype == RV_DTYPE_F32)
+        RV_LAUNCH_ST = rv_launch(paged_attention_ref_kernel<float, DPL>, dim3(grid), dim3(warps * 32), 0, stream,
+            (const float*)q, (const float*)cache, block_tables, cu_seqlens, ctx_lens, token_seq, (float*)out,
+            n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window, softcap, sinks, gate, planes, vd);
+    else if (dtype == RV_DTYPE_BF16)
+        RV_LAUNCH_ST = rv_launch(paged_attention_ref_kernel<__nv_bfloat16, DPL>, dim3(grid), dim3(warps * 32), 0, stream,
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, cu_seqlens, ctx_lens, token_seq,
+            (__nv_bfloat16*)out, n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window, softcap, sinks, gate, planes, vd);
+    else
+        return RV_ERR_BAD_DTYPE;
+    return rv_launch_status();
+}
+
+// planes 2: keys and values in their planes, output rows of hd; planes 1: the value is the leading vd elements of the key row.
+RV_EXPORT int rv_paged_attention_ref_ex(const void* q, const void* cache, const int* block_tables,
+                                        const int* cu_seqlens, const int* ctx_lens, const int* token_seq,
+                                        void* out, int n_tokens, int nh, int nkv, int hd, int page_size,
+                                        int max_blocks, float scale, int window, float softcap, const float* sinks,
+                                        const float* gate, int planes, int vd, int dtype, cudaStream_t stream) {
+    if (n_tokens < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0) return RV_ERR_BAD_SIZE;
+    if ((planes != 1 && planes != 2) || vd <= 0 || vd > hd || (planes == 2 && vd != hd)) return RV_ERR_BAD_SIZE;
+    if (hd > 32 * 32) return RV_ERR_UNSUPPORTED;
+    if (n_tokens == 0) return RV_OK;
+    if (hd <= 32 * 8)
+        return launch_ref<8>(q, cache, block_tables, cu_seqlens, ctx_lens, token_seq, out, n_tokens, nh, nkv, hd, page_size,
+                             max_blocks, scale, window, softcap, sinks, gate, planes, vd, dtype, stream);
+    return launch_ref<32>(q, cache, block_tables, cu_seqlens, ctx_lens, token_seq, out, n_tokens, nh, nkv, hd, page_size,
+                          max_blocks, scale, window, softcap, sinks, gate, planes, vd, dtype, stream);
 }
 
 RV_EXPORT int rv_paged_attention_ref(const void* q, const void* cache, const int* block_tables,
@@ -102,20 +141,7 @@ RV_EXPORT int rv_paged_attention_ref(const void* q, const void* cache, const int
                                      void* out, int n_tokens, int nh, int nkv, int hd, int page_size,
                                      int max_blocks, float scale, int window, float softcap, const float* sinks,
                                      const float* gate, int dtype, cudaStream_t stream) {
-    if (n_tokens < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0) return RV_ERR_BAD_SIZE;
-    if (hd > 32 * MAX_DIMS_PER_LANE) return RV_ERR_UNSUPPORTED;
-    if (n_tokens == 0) return RV_OK;
-    const int warps = 4;
-    const dim3 grid(n_tokens, (nh + warps - 1) / warps);
-    if (dtype == RV_DTYPE_F32)
-        RV_LAUNCH_ST = rv_launch(paged_attention_ref_kernel<float>, dim3(grid), dim3(warps * 32), 0, stream, 
-            (const float*)q, (const float*)cache, block_tables, cu_seqlens, ctx_lens, token_seq, (float*)out,
-            n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window, softcap, sinks, gate);
-    else if (dtype == RV_DTYPE_BF16)
-        RV_LAUNCH_ST = rv_launch(paged_attention_ref_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, 
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, cu_seqlens, ctx_lens, token_seq,
-            (__nv_bfloat16*)out, n_tokens, nh, nkv, hd, page_size, max_blocks, scale, window, softcap, sinks, gate);
-    else
-        return RV_ERR_BAD_DTYPE;
-    return rv_launch_status();
+    if (hd > 32 * 8) return RV_ERR_UNSUPPORTED;
+    return rv_paged_attention_ref_ex(q, cache, block_tables, cu_seqlens, ctx_lens, token_seq, out, n_tokens, nh, nkv, hd,
+                                     page_size, max_blocks, scale, window, softcap, sinks, gate, 2, hd, dtype, stream);
 }

@@ -1,0 +1,149 @@
+// A mixture of gated experts whose choice per token is given (a table lookup by token id, a router's top-k): every
+// token runs `top` experts  down_e( silu(gate_e x) * up_e x )  and adds them with one weight.
+//
+// Layout: gate_up [experts, 2 ff, width] (an expert's gate rows, then its up rows), down [experts, width, ff],
+// chosen [tokens, top] int32 expert numbers (numbers outside 0 .. experts-1 contribute nothing).
+//
+//   moe_gate_up   act[t * top + k, f] = silu(gate_e[f] . x_t) * (up_e[f] . x_t),  e = chosen[t, k]
+//   moe_down      out[t, n] = (add[t, n]) + weight * sum_k down_e(k)[n] . act[t * top + k]
+//
+// One CTA per (token, slot) and block of features keeps the token's vector in shared memory as float; a warp owns a
+// feature at a time and its lanes walk the weight row (16-byte loads where rows are aligned).  The weights of an
+// expert are read once per token that chose it: the kernels serve decoded tokens and short portions, where the step
+// is bound by reading the chosen experts' weights; sums are float, in one order whatever the batch.
+#include "common.cuh"
+
+template <typename T> __device__ __forceinline__ float moe_dot(const T* __restrict__ w, const float* __restrict__ x, int n, int lane);
+
+template <> __device__ __forceinline__ float moe_dot<float>(const float* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    float s = 0.f;
+    if ((n & 3) == 0 && ((uintptr_t)w & 15) == 0) {
+        for (int i = lane * 4; i < n; i += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(w + i);
+            s = fmaf(v.x, x[i], s); s = fmaf(v.y, x[i + 1], s); s = fmaf(v.z, x[i + 2], s); s = fmaf(v.w, x[i + 3], s);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) s = fmaf(w[i], x[i], s);
+    }
+    return rv_warp_sum(s);
+}
+
+template <> __device__ __forceinline__ float moe_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    float s = 0.f;
+    if ((n & 7) == 0 && ((uintptr_t)w & 15) == 0) {
+        for (int i = lane * 8; i < n; i += 256) {
+            const uint4 v = *reinterpret_cast<const uint4*>(w + i);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(p[j]);
+                s = fmaf(f.x, x[i + 2 * j], s); s = fmaf(f.y, x[i + 2 * j + 1], s);
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) s = fmaf(__bfloat162float(w[i]), x[i], s);
+    }
+    return rv_warp_sum(s);
+}
+
+#define MOE_WARPS 8
+#define MOE_FEATURES 32      // features of one CTA
+
+// grid (tokens * top, feature blocks)
+template <typename T>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ chosen, const T* __restrict__ gate_up, T* __restrict__ act,
+                   int top, int experts, int ff, int width) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    extern __shared__ float xs[];
+    const int pair = blockIdx.x, t = pair / top;
+    const int e = chosen[pair];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int f0 = blockIdx.y * MOE_FEATURES;
+    if (e < 0 || e >= experts) {
+        for (int f = f0 + threadIdx.x; f < min(ff, f0 + MOE_FEATURES); f += blockDim.x) act[(size_t)pair * ff + f] = rv_from_float<T>(0.f);
+        return;
+    }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = rv_to_float(x[(size_t)t * width + i]);
+    __syncthreads();
+    const T* wg = gate_up + (size_t)e * 2 * ff * width;
+    const T* wu = wg + (size_t)ff * width;
+    for (int f = f0 + warp; f < min(ff, f0 + MOE_FEATURES); f += MOE_WARPS) {
+        const float g = moe_dot<T>(wg + (size_t)f * width, xs, width, lane);
+        const float u = moe_dot<T>(wu + (size_t)f * width, xs, width, lane);
+        if (lane == 0) act[(size_t)pair * ff + f] = rv_from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+// grid (tokens, feature blocks)
+template <typename T, typename TO>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_down_kernel(const T* __restrict__ act, const int* __restrict__ chosen, const T* __restrict__ down, const float* add,
+                TO* out, int top, int experts, int ff, int width, float weight) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    extern __shared__ float as[];                 // [top][ff]
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < top * ff; i += blockDim.x) as[i] = rv_to_float(act[(size_t)t * top * ff + i]);
+    __syncthreads();
+    const int n0 = blockIdx.y * MOE_FEATURES;
+    for (int n = n0 + warp; n < min(width, n0 + MOE_FEATURES); n += MOE_WARPS) {
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int e = chosen[t * top + k];
+            if (e < 0 || e >= experts) continue;
+            s += moe_dot<T>(down + ((size_t)e * width + n) * ff, as + (size_t)k * ff, ff, lane);
+        }
+        if (lane == 0) {
+            float v = s * weight;
+            if (add) v += add[(size_t)t * width + n];
+            out[(size_t)t * width + n] = rv_from_float<TO>(v);
+        }
+    }
+}
+
+static RvPerDevice g_once[6];
+
+template <typename T>
+static int moe_launch(const void* x, const int* chosen, const void* gate_up, const void* down, void* act, const float* add,
+                      void* out, int out_f32, int tokens, int top, int experts, int ff, int width, float weight,
+                      int slot, cudaStream_t stream) {
+    const int smem_a = width * 4, smem_b = top * ff * 4;
+    if (smem_a > 200 * 1024 || smem_b > 200 * 1024) return RV_ERR_UNSUPPORTED;
+    int st = rv_configure_smem(g_once[slot], moe_gate_up_kernel<T>, 200 * 1024);
+    if (st != RV_OK) return st;
+    RV_LAUNCH_ST = rv_launch(moe_gate_up_kernel<T>, dim3(tokens * top, (ff + MOE_FEATURES - 1) / MOE_FEATURES), dim3(MOE_WARPS * 32),
+                             (size_t)smem_a, stream, (const T*)x, chosen, (const T*)gate_up, (T*)act, top, experts, ff, width);
+    st = rv_launch_status();
+    if (st != RV_OK) return st;
+    const dim3 grid(tokens, (width + MOE_FEATURES - 1) / MOE_FEATURES);
+    if (out_f32) {
+        st = rv_configure_smem(g_once[slot + 1], moe_down_kernel<T, float>, 200 * 1024);
+        if (st != RV_OK) return st;
+        RV_LAUNCH_ST = rv_launch(moe_down_kernel<T, float>, dim3(grid), dim3(MOE_WARPS * 32), (size_t)smem_b, stream, (const T*)act,
+                                 chosen, (const T*)down, add, (float*)out, top, experts, ff, width, weight);
+    } else {
+        st = rv_configure_smem(g_once[slot + 2], moe_down_kernel<T, T>, 200 * 1024);
+        if (st != RV_OK) return st;
+        RV_LAUNCH_ST = rv_launch(moe_down_kernel<T, T>, dim3(grid), dim3(MOE_WARPS * 32), (size_t)smem_b, stream, (const T*)act,
+                                 chosen, (const T*)down, add, (T*)out, top, experts, ff, width, weight);
+    }
+    return rv_launch_status();
+}
+
+// x [tokens, width], act [tokens * top, ff] (scratch of the weights' type), add float [tokens, width] or null,
+// out [tokens, width] float (out_f32) or of the weights' type.  Two launches.
+RV_EXPORT int rv_moe_experts(const void* x, const int* chosen, const void* gate_up, const void* down, void* act, const float* add,
+                             void* out, int out_f32, int tokens, int top, int experts, int ff, int width, float weight,
+                             int dtype, cudaStream_t stream) {
+    if (tokens < 0 || top <= 0 || experts <= 0 || ff <= 0 || width <= 0) return RV_ERR_BAD_SIZE;
+    if ((long long)tokens * top > 0x7fffffffLL || ff > 65535 * MOE_FEATURES || width > 65535 * MOE_FEATURES) return RV_ERR_BAD_SIZE;
+    if (tokens == 0) return RV_OK;
+    if (dtype == RV_DTYPE_F32)
+        return moe_launch<float>(x, chosen, gate_up, down, act, add, out, 1, tokens, top, experts, ff, width, weight, 0, stream);
+    if (dtype == RV_DTYPE_BF16)
+        return moe_launch<__nv_bfloat16>(x, chosen, gate_up, down, act, add, out, out_f32, tokens, top, experts, ff, width, weight, 3, stream);
+    return RV_ERR_BAD_DTYPE;
+}

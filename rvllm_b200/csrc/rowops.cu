@@ -3,6 +3,11 @@
 //
 //   residual_rmsnorm      r <- r + y / sqrt(mean(y^2) + eps) * gamma   (r float32; also a copy of the new r
 //                         in the activations' type, which the next sublayer's products read)
+//                         with a second norm (weight, eps) the copy is the new r under THAT norm: the input of the next sublayer
+//                         of a layer that normalises in front of and behind every sublayer
+//   stream_add            x += (e) + v: what a model adds to the stream between two runs of a span of layers
+//   polynorm              a n(z) + b n(z^2) + c n(z^3) + e, n = division by the row's root mean square
+//   softcap               x <- c tanh(x / c) on float logits
 //   act_mul               rows [gate | up] -> act(gate) * up, act = SiLU or the tanh form of GELU
 //   qk_norm_rope_write    rows [q | k | gate logits]: q and k each divided by the root mean square of their
 //                         WHOLE row part and multiplied by a weight of that width, the leading `rot` elements
@@ -26,7 +31,7 @@ __device__ __forceinline__ void rv_store_any(void* p, int dtype, size_t i, float
 __global__ void __launch_bounds__(256)
 residual_rmsnorm_kernel(const void* __restrict__ y, int y_dtype, const void* __restrict__ gamma, int gamma_dtype,
                         const float* res_in, float* res_out, void* __restrict__ rounded, int rounded_dtype,
-                        int cols, float eps) {
+                        int cols, float eps, const void* __restrict__ next_gamma, int next_dtype, float next_eps) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     __shared__ float scratch[33];
@@ -38,22 +43,120 @@ residual_rmsnorm_kernel(const void* __restrict__ y, int y_dtype, const void* __r
     }
     ss = rv_block_sum(ss, scratch);
     const float r = 1.0f / sqrtf(ss / (float)cols + eps);
+    if (!next_gamma) {
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+            float v = rv_load_any(y, y_dtype, base + i) * r * rv_load_param(gamma, gamma_dtype, i);
+            if (res_in) v += res_in[base + i];
+            if (res_out) res_out[base + i] = v;
+            if (rounded) rv_store_any(rounded, rounded_dtype, base + i, v);
+        }
+        return;
+    }
+    // the new stream is written, its own mean square gathered on the way, and the copy for the next sublayer is the
+    // new stream under that sublayer's norm (every thread reads back what it wrote itself)
+    float s2 = 0.f;
     for (int i = threadIdx.x; i < cols; i += blockDim.x) {
         float v = rv_load_any(y, y_dtype, base + i) * r * rv_load_param(gamma, gamma_dtype, i);
         if (res_in) v += res_in[base + i];
-        if (res_out) res_out[base + i] = v;
-        if (rounded) rv_store_any(rounded, rounded_dtype, base + i, v);
+        res_out[base + i] = v;
+        s2 = fmaf(v, v, s2);
     }
+    s2 = rv_block_sum(s2, scratch);
+    const float r2 = 1.0f / sqrtf(s2 / (float)cols + next_eps);
+    for (int i = threadIdx.x; i < cols; i += blockDim.x)
+        rv_store_any(rounded, rounded_dtype, base + i, res_out[base + i] * r2 * rv_load_param(next_gamma, next_dtype, i));
+}
+
+RV_EXPORT int rv_residual_rmsnorm_next(const void* y, int y_dtype, const void* gamma, int gamma_dtype, const float* res_in,
+                                       float* res_out, void* rounded, int rounded_dtype, int rows, int cols, float eps,
+                                       const void* next_gamma, int next_dtype, float next_eps, cudaStream_t stream) {
+    if (rows < 0 || cols <= 0) return RV_ERR_BAD_SIZE;
+    if ((y_dtype | gamma_dtype | rounded_dtype | next_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (next_gamma && (!res_out || !rounded)) return RV_ERR_UNSUPPORTED;
+    if (rows == 0) return RV_OK;
+    RV_LAUNCH_ST = rv_launch(residual_rmsnorm_kernel, dim3(rows), dim3(cols >= 1024 ? 256 : 128), 0, stream, y, y_dtype, gamma,
+                             gamma_dtype, res_in, res_out, rounded, rounded_dtype, cols, eps, next_gamma, next_dtype, next_eps);
+    return rv_launch_status();
 }
 
 RV_EXPORT int rv_residual_rmsnorm(const void* y, int y_dtype, const void* gamma, int gamma_dtype, const float* res_in,
                                   float* res_out, void* rounded, int rounded_dtype, int rows, int cols, float eps,
                                   cudaStream_t stream) {
+    return rv_residual_rmsnorm_next(y, y_dtype, gamma, gamma_dtype, res_in, res_out, rounded, rounded_dtype, rows, cols, eps,
+                                    nullptr, 0, 0.f, stream);
+}
+
+// ------------------------------------------------------------------ additions to the stream, PolyNorm, capped logits
+// x[t, :] += (e[t, :]) + v[:], float32 stream; e optional; v a row of a parameter table in either type.
+__global__ void stream_add_kernel(float* __restrict__ x, const float* __restrict__ e, const void* __restrict__ v, int v_dtype,
+                                  int cols, size_t total) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float a = x[i] + rv_load_param(v, v_dtype, (int)(i % cols));
+        if (e) a += e[i];
+        x[i] = a;
+    }
+}
+
+RV_EXPORT int rv_stream_add(float* x, const float* e, const void* v, int v_dtype, int rows, int cols, cudaStream_t stream) {
     if (rows < 0 || cols <= 0) return RV_ERR_BAD_SIZE;
-    if ((y_dtype | gamma_dtype | rounded_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (v_dtype & ~1) return RV_ERR_BAD_DTYPE;
     if (rows == 0) return RV_OK;
-    RV_LAUNCH_ST = rv_launch(residual_rmsnorm_kernel, dim3(rows), dim3(cols >= 1024 ? 256 : 128), 0, stream, y, y_dtype, gamma,
-                             gamma_dtype, res_in, res_out, rounded, rounded_dtype, cols, eps);
+    const size_t total = (size_t)rows * cols;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    RV_LAUNCH_ST = rv_launch(stream_add_kernel, dim3(blocks), dim3(256), 0, stream, x, e, v, v_dtype, cols, total);
+    return rv_launch_status();
+}
+
+// out = a n(z) + b n(z^2) + c n(z^3) + e, n(v) = v / sqrt(mean(v^2) + eps) over the row; coef = (a, b, c, e) float.
+__global__ void __launch_bounds__(256)
+polynorm_kernel(const void* __restrict__ z, int z_dtype, const float* __restrict__ coef, void* __restrict__ out, int out_dtype,
+                int cols, float eps) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * cols;
+    float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float v = rv_load_any(z, z_dtype, base + i), v2 = v * v, v3 = v2 * v;
+        s1 = fmaf(v, v, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+    }
+    s1 = rv_block_sum(s1, scratch);
+    s2 = rv_block_sum(s2, scratch);
+    s3 = rv_block_sum(s3, scratch);
+    const float n = (float)cols;
+    const float a = coef[0] / sqrtf(s1 / n + eps), b = coef[1] / sqrtf(s2 / n + eps), c = coef[2] / sqrtf(s3 / n + eps), e = coef[3];
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float v = rv_load_any(z, z_dtype, base + i), v2 = v * v;
+        rv_store_any(out, out_dtype, base + i, a * v + b * v2 + c * (v2 * v) + e);
+    }
+}
+
+RV_EXPORT int rv_polynorm(const void* z, int z_dtype, const float* coef, void* out, int out_dtype, int rows, int cols, float eps,
+                          cudaStream_t stream) {
+    if (rows < 0 || cols <= 0) return RV_ERR_BAD_SIZE;
+    if ((z_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (rows == 0) return RV_OK;
+    RV_LAUNCH_ST = rv_launch(polynorm_kernel, dim3(rows), dim3(cols >= 1024 ? 256 : 128), 0, stream, z, z_dtype, coef, out, out_dtype,
+                             cols, eps);
+    return rv_launch_status();
+}
+
+// x <- cap * tanh(x / cap), float, in place.
+__global__ void softcap_kernel(float* __restrict__ x, float cap, size_t total) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    const float inv = 1.0f / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+
+RV_EXPORT int rv_softcap(float* x, float cap, long long total, cudaStream_t stream) {
+    if (total < 0 || !(cap > 0.f)) return RV_ERR_BAD_SIZE;
+    if (total == 0) return RV_OK;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    RV_LAUNCH_ST = rv_launch(softcap_kernel, dim3(blocks), dim3(256), 0, stream, x, cap, (size_t)total);
     return rv_launch_status();
 }
 

@@ -18,7 +18,7 @@ from ..kernels import get_library
 from ..models import DecoderModel
 from ..parts.base import KvCacheNeed
 from ..weights import WeightSource
-from ..weights.random_init import INIT_STD
+from ..weights.random_init import INIT_STD, random_choice_table
 from .step import ModelRunner
 
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -53,6 +53,10 @@ class Engine:
 
                 def get(name: str) -> torch.Tensor:
                     ts = expected[name]
+                    if ts.init.startswith("choice:"):        # an integer table: drawn on the host, keyed like the others
+                        gen = torch.Generator()
+                        gen.manual_seed((seed << 20) + order[name])
+                        return random_choice_table(ts.shape, ts.init, gen).to(self.device)
                     mean, std = INIT_STD[ts.init]
                     return self.kernels.fill_normal(ts.shape, self.dtype, mean, std, seed, order[name])
             else:
@@ -61,6 +65,8 @@ class Engine:
 
                 def get(name: str) -> torch.Tensor:
                     ts = expected[name]
+                    if ts.init.startswith("choice:"):
+                        return random_choice_table(ts.shape, ts.init, gen)
                     mean, std = INIT_STD[ts.init]
                     t = torch.empty(ts.shape, dtype=torch.float32, device=self.device).normal_(mean, std, generator=gen)
                     return t.to(self.dtype)

@@ -169,6 +169,8 @@ class CudaKernels:
     def gather_rows(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         """out[t] = table[ids[t]]; ids int32.  Used for the embedding and for picking logit rows."""
         _need(table, "table", dims=2); _need(ids, "ids", torch.int32, 1)
+        if table.dtype == torch.int32:          # an integer table (which experts a token id uses): its rows are copied as 32-bit words
+            return self.gather_rows(table.view(torch.float32), ids).view(torch.int32)
         out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
         st = self._lib("elementwise.cu").rv_gather_rows(
             _ptr(table), _ptr(ids), _ptr(out), c_int(ids.shape[0]), c_int(table.shape[1]),
@@ -823,10 +825,11 @@ class CudaKernels:
 
     # ------------------------------------------------------------------ output-norm layers, gated attention, state-space mixer
     def residual_rmsnorm(self, y, gamma, eps: float, residual: Optional[torch.Tensor], rounded_dtype=None,
-                         keep_residual: bool = True):
+                         keep_residual: bool = True, next_norm=None):
         """r = residual + y / sqrt(mean(y^2) + eps) * gamma in float32 (residual None: zero).  Returns
         (r as float32 [rows, cols] or None without `keep_residual`, r rounded to `rounded_dtype` or None).
-        `residual` is updated in place when given."""
+        `residual` is updated in place when given.  next_norm = (gamma', eps'): the second result is not r itself
+        but r / sqrt(mean(r^2) + eps') * gamma' in `rounded_dtype`, the input of a sublayer that normalises what it reads."""
         _need(y, "y", dims=2); _need(gamma, "gamma", dims=1)
         rows, cols = y.shape
         if gamma.shape[0] != cols:
@@ -839,6 +842,19 @@ class CudaKernels:
         if keep_residual:
             res_out = residual if residual is not None else torch.empty((rows, cols), dtype=torch.float32, device=y.device)
         rounded = None
+        if next_norm is not None:
+            if rounded_dtype is None or not keep_residual:
+                raise KernelError("residual_rmsnorm: a following norm needs the stream kept and a type for its result")
+            _need(next_norm[0], "next gamma", dims=1)
+            if next_norm[0].shape[0] != cols:
+                raise KernelError(f"residual_rmsnorm: the following norm has {next_norm[0].shape[0]} entries for rows of {cols}")
+            rounded = torch.empty((rows, cols), dtype=rounded_dtype, device=y.device)
+            st = self._lib("rowops.cu").rv_residual_rmsnorm_next(
+                _ptr(y), c_int(self._dt(y, "y")), _ptr(gamma), c_int(self._dt(gamma, "gamma")), _ptr(residual), _ptr(res_out),
+                _ptr(rounded), c_int(_DT[rounded_dtype]), c_int(rows), c_int(cols), c_float(eps), _ptr(next_norm[0]),
+                c_int(self._dt(next_norm[0], "next gamma")), c_float(next_norm[1]), self._stream())
+            _check("residual_rmsnorm", st)
+            return res_out, rounded
         if rounded_dtype is not None and not (rounded_dtype == torch.float32 and keep_residual):
             rounded = torch.empty((rows, cols), dtype=rounded_dtype, device=y.device)
         st = self._lib("rowops.cu").rv_residual_rmsnorm(
@@ -980,6 +996,145 @@ class CudaKernels:
             _ptr(y), _ptr(proj), c_int(self._dt(proj, "proj")), c_int(proj.shape[1]), _ptr(gamma), c_int(self._dt(gamma, "gamma")),
             _ptr(out), c_int(_DT[out_dtype]), c_int(rows), c_int(width), c_int(parts), c_float(eps), self._stream())
         _check("gated_group_rmsnorm", st)
+        return out
+
+
+    # ------------------------------------------------------------------ stream additions, PolyNorm, capped logits
+    def stream_add(self, x, emb: Optional[torch.Tensor], table: torch.Tensor, index: int) -> torch.Tensor:
+        """x += (emb) + table[index] on the float32 stream, in place; returns x."""
+        _need(x, "x", torch.float32, 2); _need(table, "table", dims=2)
+        if table.shape[1] != x.shape[1] or not 0 <= index < table.shape[0]:
+            raise KernelError(f"stream_add: row {index} of a table {tuple(table.shape)} for rows of {x.shape[1]}")
+        if emb is not None:
+            _need(emb, "emb", torch.float32, 2)
+            if emb.shape != x.shape:
+                raise KernelError(f"stream_add: {tuple(emb.shape)} added to {tuple(x.shape)}")
+        row = table[index]
+        st = self._lib("rowops.cu").rv_stream_add(_ptr(x), _ptr(emb), _ptr(row), c_int(self._dt(row, "table")), c_int(x.shape[0]),
+                                                  c_int(x.shape[1]), self._stream())
+        _check("stream_add", st)
+        return x
+
+    def polynorm(self, z, coef: torch.Tensor, eps: float, out_dtype=None) -> torch.Tensor:
+        """a n(z) + b n(z^2) + c n(z^3) + e per row, n(v) = v / sqrt(mean(v^2) + eps); coef = float (a, b, c, e)."""
+        _need(z, "z", dims=2); _need(coef, "coef", torch.float32, 1)
+        if coef.shape[0] != 4:
+            raise KernelError(f"polynorm: four coefficients, got {coef.shape[0]}")
+        out = torch.empty(z.shape, dtype=out_dtype or z.dtype, device=z.device)
+        st = self._lib("rowops.cu").rv_polynorm(_ptr(z), c_int(self._dt(z, "z")), _ptr(coef), _ptr(out), c_int(self._dt(out, "out")),
+                                                c_int(z.shape[0]), c_int(z.shape[1]), c_float(eps), self._stream())
+        _check("polynorm", st)
+        return out
+
+    def softcap(self, logits: torch.Tensor, cap: float) -> torch.Tensor:
+        """logits <- cap * tanh(logits / cap), float32, in place; returns logits."""
+        _need(logits, "logits", torch.float32)
+        st = self._lib("rowops.cu").rv_softcap(_ptr(logits), c_float(cap), ctypes.c_longlong(logits.numel()), self._stream())
+        _check("softcap", st)
+        return logits
+
+    # ------------------------------------------------------------------ latent attention
+    def latent_prepare(self, proj, c_gamma, eps: float, positions, cos, sin, slot_mapping, cache_layer, num_heads: int,
+                       head_dim: int, rot_dim: int, kv_rank: int, out_dtype, with_gate: bool = True, write_kv: bool = True):
+        """proj rows [q: heads x (head_dim + rot_dim) | c': kv_rank | r: rot_dim | gate logits: heads].  c' is RMS-normalised
+        (weight `c_gamma`), the leading 2 * cos.shape[1] elements of r and of every head's rotated query part are turned in
+        pairs (2i, 2i + 1), [c | r] is written into the token's cache row.  Returns (q_plain [T, heads, head_dim],
+        q_row [T, heads, kv_rank + rot_dim] with its last rot_dim columns filled, sigmoid(gate logits) float [T, heads] or None)."""
+        _need(proj, "proj", dims=2); _need(positions, "positions", torch.int32, 1); _need(c_gamma, "c_gamma", dims=1)
+        T, row = proj.shape[0], kv_rank + rot_dim
+        if proj.shape[1] != num_heads * (head_dim + rot_dim) + row + (num_heads if with_gate else 0) or c_gamma.shape[0] != kv_rank:
+            raise KernelError(f"latent_prepare: rows of {proj.shape[1]} columns do not fit {num_heads} heads of {head_dim} + {rot_dim}, "
+                              f"a latent of {kv_rank} + {rot_dim}" + (f" and {num_heads} gates" if with_gate else ""))
+        rot, table_rows = 0, 1
+        if cos is not None:
+            _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+            rot, table_rows = 2 * cos.shape[1], cos.shape[0]
+            if not 0 < rot <= rot_dim or sin.shape != cos.shape:
+                raise KernelError(f"latent_prepare: cos/sin tables must be [rows, dims/2] with dims <= {rot_dim}")
+        if write_kv:
+            _need(cache_layer, "cache_layer", out_dtype, 5); _need(slot_mapping, "slot_mapping", torch.int32, 1)
+            if tuple(cache_layer.shape[1:3]) != (1, 1) or cache_layer.shape[4] != row:
+                raise KernelError(f"latent_prepare: cache layer of shape {tuple(cache_layer.shape)} does not hold one row of {row} per token")
+        q_plain = torch.empty((T, num_heads, head_dim), dtype=out_dtype, device=proj.device)
+        q_row = torch.empty((T, num_heads, row), dtype=out_dtype, device=proj.device)
+        gate = torch.empty((T, num_heads), dtype=torch.float32, device=proj.device) if with_gate else None
+        st = self._lib("latent.cu").rv_latent_prepare(
+            _ptr(proj), c_int(self._dt(proj, "proj")), c_int(proj.shape[1]), _ptr(c_gamma), c_int(self._dt(c_gamma, "c_gamma")),
+            _ptr(positions), _ptr(cos), _ptr(sin), c_int(rot), c_int(table_rows), _ptr(slot_mapping if write_kv else None),
+            _ptr(cache_layer if write_kv else None), _ptr(q_plain), _ptr(q_row), c_int(_DT[out_dtype]), _ptr(gate), c_int(T),
+            c_int(num_heads), c_int(head_dim), c_int(rot_dim), c_int(kv_rank), c_float(eps), c_int(1 if write_kv else 0), self._stream())
+        _check("latent_prepare", st)
+        return q_plain, q_row, gate
+
+    def head_linear(self, x, weight, out: Optional[torch.Tensor] = None, out_dtype=None) -> torch.Tensor:
+        """out[t, h, :] = weight[h] x[t, h, :] for x [T, heads, K], weight [heads, N, K]; float accumulation.  x and out may be
+        slices of wider rows (their last dimension contiguous); without `out` a new [T, heads, N] tensor is returned."""
+        _need(weight, "weight", dims=3)
+        H, N, K = weight.shape
+        if x.dim() != 3 or x.shape[1] != H or x.shape[2] != K or x.stride(2) != 1 or not x.is_cuda:
+            raise KernelError(f"head_linear: x of shape {tuple(x.shape)} and strides {x.stride()} for weights {tuple(weight.shape)}")
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty((T, H, N), dtype=out_dtype or x.dtype, device=x.device)
+        if tuple(out.shape) != (T, H, N) or out.stride(2) != 1:
+            raise KernelError(f"head_linear: out of shape {tuple(out.shape)} and strides {out.stride()}, expected {(T, H, N)}")
+        st = self._lib("latent.cu").rv_head_linear(
+            _ptr(x), c_int(self._dt(x, "x")), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)), _ptr(weight),
+            c_int(self._dt(weight, "weight")), _ptr(out), c_int(self._dt(out, "out")), ctypes.c_longlong(out.stride(0)),
+            ctypes.c_longlong(out.stride(1)), c_int(T), c_int(H), c_int(N), c_int(K), self._stream())
+        _check("head_linear", st)
+        return out
+
+    def latent_attention(self, q_row, cache_layer, meta: AttentionMeta, num_heads: int, row: int, value_dim: int, scale: float,
+                         gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Attention of the step's tokens over cached rows that are key and value at once: every head's query
+        [T, heads, row] meets the whole row of a token, the weighted sum is taken over the rows' leading `value_dim`
+        elements.  Causal, softmax in float; `gate` (float [T, heads]) multiplies each head's result.  Returns
+        [T, heads, value_dim] in q's type."""
+        _need(q_row, "q_row", dims=3); _need(cache_layer, "cache_layer", q_row.dtype, 5)
+        T = q_row.shape[0]
+        if q_row.shape[1] != num_heads or q_row.shape[2] != row or tuple(cache_layer.shape[1:3]) != (1, 1) or cache_layer.shape[4] != row:
+            raise KernelError(f"latent_attention: queries {tuple(q_row.shape)} and cache {tuple(cache_layer.shape)} do not fit "
+                              f"{num_heads} heads on rows of {row}")
+        if not 0 < value_dim <= row:
+            raise KernelError(f"latent_attention: a value of {value_dim} out of a row of {row}")
+        self._check_attention_extras(q_row.view(T, -1), num_heads, None, gate)
+        out = torch.empty((T, num_heads, value_dim), dtype=q_row.dtype, device=q_row.device)
+        st = self._lib("attention_ref.cu").rv_paged_attention_ref_ex(
+            _ptr(q_row), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens),
+            _ptr(meta.token_seq), _ptr(out), c_int(T), c_int(num_heads), c_int(1), c_int(row), c_int(cache_layer.shape[3]),
+            c_int(meta.max_blocks), c_float(scale), c_int(0), c_float(0.0), _ptr(None), _ptr(gate), c_int(1), c_int(value_dim),
+            c_int(self._dt(q_row, "q_row")), self._stream())
+        _check("latent_attention", st)
+        return out
+
+    # ------------------------------------------------------------------ mixture of experts
+    def moe_experts(self, x, chosen, gate_up, down, weight: float, add: Optional[torch.Tensor] = None, out_dtype=None) -> torch.Tensor:
+        """out[t] = (add[t]) + weight * sum_k down[e] (silu(gate[e] x_t) * (up[e] x_t)), e = chosen[t, k].
+        gate_up [experts, 2 ff, width] (gate rows, then up rows), down [experts, width, ff], chosen int32 [T, top],
+        add float32 [T, width] or None."""
+        _need(x, "x", dims=2); _need(chosen, "chosen", torch.int32, 2)
+        _need(gate_up, "gate_up", x.dtype, 3); _need(down, "down", x.dtype, 3)
+        T, width = x.shape
+        E, ff2, _ = gate_up.shape
+        ff, top = ff2 // 2, chosen.shape[1]
+        if gate_up.shape[2] != width or tuple(down.shape) != (E, width, ff) or chosen.shape[0] != T or ff * 2 != ff2:
+            raise KernelError(f"moe_experts: x {tuple(x.shape)}, gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}, "
+                              f"chosen {tuple(chosen.shape)} do not fit together")
+        if add is not None:
+            _need(add, "add", torch.float32, 2)
+            if add.shape != x.shape:
+                raise KernelError(f"moe_experts: add {tuple(add.shape)} against x {tuple(x.shape)}")
+        out_dtype = out_dtype or x.dtype
+        if out_dtype not in (x.dtype, torch.float32):
+            raise KernelError(f"moe_experts: result type {out_dtype} for operands of {x.dtype}")
+        act = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
+        out = torch.empty((T, width), dtype=out_dtype, device=x.device)
+        st = self._lib("moe.cu").rv_moe_experts(
+            _ptr(x), _ptr(chosen), _ptr(gate_up), _ptr(down), _ptr(act), _ptr(add), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
+            c_int(T), c_int(top), c_int(E), c_int(ff), c_int(width), c_float(weight), c_int(self._dt(x, "x")), self._stream())
+        _check("moe_experts", st)
+        COUNTERS['launches'] += 1
         return out
 
     # ------------------------------------------------------------------ sampling

@@ -59,6 +59,9 @@ class DecoderModel:
         self.final_norm = NORMS.build(spec.final_norm.kind, **spec.final_norm.params)
         self.embedding_hooks = [HOOKS.build(h.kind, **h.params) for h in spec.embedding_hooks]
         self.logit_hooks = [HOOKS.build(h.kind, **h.params) for h in spec.logit_hooks]
+        # hooks on the stream in front of a run entry (what a model adds at the start of a repeated pass)
+        self.entry_hooks = [[HOOKS.build(h.kind, **h.params) for h in e.before] for e in spec.run_order]
+        self.keeps_embedding_output = any(getattr(h, "needs_embedding_output", False) for hs in self.entry_hooks for h in hs)
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
         self.dtype = None
@@ -74,6 +77,8 @@ class DecoderModel:
             out.append((f"position.{key}.", pe))
         out.extend((f"hooks.embedding.{i}.", h) for i, h in enumerate(self.embedding_hooks))
         out.extend((f"hooks.logits.{i}.", h) for i, h in enumerate(self.logit_hooks))
+        # (a hook in front of a run entry names its tensors in full: several entries may share one)
+        out.extend(("", h) for hs in self.entry_hooks for h in hs)
         return out
 
     @property
@@ -131,7 +136,12 @@ class DecoderModel:
         ctx.extras["activation_dtype"] = self.dtype
         if self.spec.residual_dtype == "float32" and x.dtype != torch.float32:
             x = x.float()              # the stream between the layers stays in 32 bits; blocks round a copy for their products
-        for e in self.spec.run_order:
+        if self.keeps_embedding_output:
+            # blocks add into the stream in place: what the embedding section left is kept as a copy
+            ctx.extras["embedding_output"] = x.clone()
+        for e, hooks in zip(self.spec.run_order, self.entry_hooks):
+            for hook in hooks:
+                x = hook(x, ctx)
             x = self.layers[e.layer].block(x, ctx, caches.view(e.cache), e.writes_cache)
         return x
 

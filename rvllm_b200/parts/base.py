@@ -39,10 +39,13 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class KvCacheNeed:
-    """Paged keys and values; `window` None keeps every key, W keeps the last W."""
+    """Paged keys and values; `window` None keeps every key, W keeps the last W.  `planes` is 2 for
+    separate key and value rows, 1 for mixers that keep ONE row per token and head from which both are
+    read (a latent that keys and values are projections of)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)

@@ -100,3 +100,43 @@ class OutputNormResidualBlock:
 
 
 BLOCKS.register("output_norm_residual", OutputNormResidualBlock)
+
+
+class SandwichNormResidualBlock:
+    """`sandwich_norm_residual`: x + norm_out(mixer(norm_in(x))), then x + norm_out'(feed_forward(norm_in'(x))): every
+    sublayer has an RMSNorm in front of it and one on what it returns.  A layer may have no feed-forward.
+
+    The stream x is float32 whatever the engine's type (`ModelSpec.residual_dtype`); sublayers are asked for a float32
+    result, which is normalised and added in 32 bits.  One kernel does the sum and the norm in front of the NEXT sublayer
+    of the layer (two row statistics in one pass over the row), and leaves that sublayer's input in the activations' type."""
+    ROLES = ("mixer", "mixer_norm", "mixer_out_norm")
+    OPTIONAL = ("feed_forward", "feed_forward_norm", "feed_forward_out_norm")
+
+    def __init__(self, parts):
+        from ..errors import ConfigError
+        names = set(parts)
+        n_opt = sum(1 for r in self.OPTIONAL if r in names)
+        if not set(self.ROLES) <= names or not names <= set(self.ROLES + self.OPTIONAL) or n_opt not in (0, len(self.OPTIONAL)):
+            raise ConfigError(f"the sandwich-norm residual block arranges {', '.join(self.ROLES)} and, together, "
+                              f"{', '.join(self.OPTIONAL)}; got {', '.join(sorted(parts))}")
+        self.mixer, self.mixer_norm, self.mixer_out_norm = (parts[r] for r in self.ROLES)
+        self.feed_forward, self.feed_forward_norm, self.feed_forward_out_norm = (parts.get(r) for r in self.OPTIONAL)
+        for n in (self.mixer_norm, self.mixer_out_norm, self.feed_forward_norm, self.feed_forward_out_norm):
+            if n is not None and not hasattr(n, "as_rms"):
+                raise ConfigError("the sandwich-norm residual block needs norms that offer `as_rms()` (an RMSNorm)")
+
+    def __call__(self, x, ctx, cache, write_cache=True):
+        k = ctx.kernels
+        dtype = ctx.extras.get("activation_dtype", x.dtype)
+        if x.dtype != torch.float32:
+            x = x.float()
+        h = k.rmsnorm(x, *self.mixer_norm.as_rms(), out_dtype=dtype)
+        y = self.mixer(h, ctx, cache, residual=None, write_cache=write_cache, out_dtype=torch.float32)
+        if self.feed_forward is None:
+            return k.residual_rmsnorm(y, *self.mixer_out_norm.as_rms(), x, None)[0]
+        x, h = k.residual_rmsnorm(y, *self.mixer_out_norm.as_rms(), x, dtype, next_norm=self.feed_forward_norm.as_rms())
+        y = self.feed_forward(h, ctx, residual=None, out_dtype=torch.float32)
+        return k.residual_rmsnorm(y, *self.feed_forward_out_norm.as_rms(), x, None)[0]
+
+
+BLOCKS.register("sandwich_norm_residual", SandwichNormResidualBlock)

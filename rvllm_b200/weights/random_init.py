@@ -2,7 +2,8 @@
 configuration and a seed.
 
 Distributions: matrices N(0, 0.02), norm weights 1 + N(0, 0.1), biases N(0, 0.02), taps of a
-short convolution N(0, 0.3).  The
+short convolution N(0, 0.3), coefficients of an activation 0.5 + N(0, 0.3); an init kind "choice:E" is an
+integer table whose rows hold distinct numbers below E (which experts a token id uses).  The
 reference has no such mode (its benchmarks run on uninitialised caches,
 v3/crates/rvllm-runtime/src/bring_up.rs:395-404); these are the distributions this
 project's benchmark configurations name.  Tensors are drawn in sorted name order from one
@@ -18,7 +19,15 @@ import torch
 
 from .safetensors_io import write_safetensors
 
-INIT_STD = {"matrix": (0.0, 0.02), "norm": (1.0, 0.1), "bias": (0.0, 0.02), "conv_taps": (0.0, 0.3)}
+INIT_STD = {"matrix": (0.0, 0.02), "norm": (1.0, 0.1), "bias": (0.0, 0.02), "conv_taps": (0.0, 0.3), "coef": (0.5, 0.3)}
+
+
+def random_choice_table(shape, init: str, gen: torch.Generator) -> torch.Tensor:
+    """int32 [rows, top]: every row holds `top` distinct numbers below E, for an init kind "choice:E"."""
+    experts = int(init.split(":", 1)[1])
+    rows, top = shape
+    scores = torch.rand((rows, experts), generator=gen, device=gen.device)
+    return scores.argsort(dim=1)[:, :top].to(torch.int32).contiguous()
 
 
 def random_tensors(tensor_specs: Dict[str, "TensorSpec"], seed: int, dtype: torch.dtype,
@@ -28,6 +37,9 @@ def random_tensors(tensor_specs: Dict[str, "TensorSpec"], seed: int, dtype: torc
     out = {}
     for name in sorted(tensor_specs):
         spec = tensor_specs[name]
+        if spec.init.startswith("choice:"):
+            out[name] = random_choice_table(spec.shape, spec.init, gen)
+            continue
         mean, std = INIT_STD[spec.init]
         t = torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(mean, std, generator=gen)
         out[name] = t.to(dtype)
