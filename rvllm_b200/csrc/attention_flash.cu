@@ -22,6 +22,21 @@
 #define HEAD_DIM 128
 #endif
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head_dim must be a multiple of 16 up to 256");
+// A build for mixers that keep ONE row per token and kv head, read as the key in full and as the value in its leading
+// V_DIM elements (-DKV_PLANES=1 -DV_DIM=n): the cache layer is [num_pages, 1, nkv, page_size, HEAD_DIM], a key tile in
+// shared memory is also the value tile, and a head's output row has V_DIM elements.  Only the cp.async kernel of this
+// file (prompt portions and split decode) serves such a build; the default is two planes and V_DIM = HEAD_DIM.
+#ifndef V_DIM
+#define V_DIM HEAD_DIM
+#endif
+#ifndef KV_PLANES
+#define KV_PLANES 2
+#endif
+static_assert(V_DIM % 16 == 0 && V_DIM >= 16 && V_DIM <= HEAD_DIM, "the value width is a multiple of 16 up to head_dim");
+static_assert(KV_PLANES == 2 || KV_PLANES == 1, "one or two planes");
+static_assert(KV_PLANES == 1 || V_DIM == HEAD_DIM, "with two planes keys and values have the same width");
+#define RV_STANDARD_KV (KV_PLANES == 2 && V_DIM == HEAD_DIM)
+#define STAGE_TILES KV_PLANES      // tiles of shared memory per stage: keys and values, or one that is both
 
 #define KV_TILE 64
 #ifndef DECODE_STAGES
@@ -164,9 +179,10 @@ flash_paged_kernel(const FlashParams p) {
     const int t_begin = tile_lo + split * per_split;
     const int t_end = min(tile_hi, t_begin + per_split);
 
-    float o[HD / 8][4];
+    constexpr int VD = V_DIM;
+    float o[VD / 8][4];
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    for (int n = 0; n < VD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     const int* table = p.block_tables + (size_t)seq * p.max_blocks;
@@ -193,12 +209,12 @@ flash_paged_kernel(const FlashParams p) {
             qa[ks][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
         }
     }
-    const size_t page_stride = (size_t)2 * p.nkv * p.page_size * HD;
+    const size_t page_stride = (size_t)KV_PLANES * p.nkv * p.page_size * HD;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
     const __nv_bfloat16* kv_base = p.cache + (size_t)kvh * p.page_size * HD;
 
     auto load_tile = [&](int t, int stage) {
-        unsigned char* ks = smem + (size_t)stage * 2 * TILE_BYTES;
+        unsigned char* ks = smem + (size_t)stage * STAGE_TILES * TILE_BYTES;
         unsigned char* vs = ks + TILE_BYTES;
         for (int idx = tid; idx < KV_TILE * CHUNKS; idx += NTHREADS) {
             const int row = idx / CHUNKS, c = idx - row * CHUNKS;
@@ -211,7 +227,7 @@ flash_paged_kernel(const FlashParams p) {
                 src = kv_base + (size_t)page * page_stride + (size_t)(key & (p.page_size - 1)) * HD + c * 8;
             }
             cp_async_16(ks + row * ROW_BYTES + c * 16, src, ok);
-            cp_async_16(vs + row * ROW_BYTES + c * 16, ok ? src + v_off : src, ok);
+            if (KV_PLANES == 2) cp_async_16(vs + row * ROW_BYTES + c * 16, ok ? src + v_off : src, ok);
         }
     };
 
@@ -227,8 +243,8 @@ flash_paged_kernel(const FlashParams p) {
         cp_async_commit();
         cp_async_wait<NSTAGES - 1>();
         __syncthreads();
-        const unsigned char* ks = smem + (size_t)stage * 2 * TILE_BYTES;
-        const unsigned char* vs = ks + TILE_BYTES;
+        const unsigned char* ks = smem + (size_t)stage * STAGE_TILES * TILE_BYTES;
+        const unsigned char* vs = KV_PLANES == 2 ? ks + TILE_BYTES : ks;      // one plane: the key rows' leading part is the value
 
         // S = Q K^T for this warp's rows and its KW keys of the tile
         float s[KW / 8][4];
@@ -284,7 +300,7 @@ flash_paged_kernel(const FlashParams p) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + l_tile[i];
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) {
+        for (int n = 0; n < VD / 8; ++n) {
             o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
             o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
         }
@@ -297,7 +313,7 @@ flash_paged_kernel(const FlashParams p) {
             pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
             pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-            for (int n2 = 0; n2 < HD / 16; ++n2) {
+            for (int n2 = 0; n2 < VD / 16; ++n2) {
                 uint32_t b[4];
                 const int key_row = warp_n * KW + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
                 const int col = n2 * 16 + (lane >> 4) * 8;
@@ -322,16 +338,16 @@ flash_paged_kernel(const FlashParams p) {
         // key/value buffers are free now), then all threads of the CTA share the work of adding
         // them up, one output element at a time, and write the result.  WARPS_M is 1 here.
         __syncthreads();
-        float* mo = reinterpret_cast<float*>(smem);                 // [WARPS_N][16][HD]
-        float* mml = mo + WARPS_N * 16 * HD;                        // [WARPS_N][16][2]
+        float* mo = reinterpret_cast<float*>(smem);                 // [WARPS_N][16][VD]
+        float* mml = mo + WARPS_N * 16 * VD;                        // [WARPS_N][16][2]
         const int n_rows = min(16, rows_total - row0);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int row = quad + 8 * i;
             if (row >= n_rows) continue;
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n) {
-                float* dst = mo + ((size_t)warp_n * 16 + row) * HD + n * 8 + tq * 2;
+            for (int n = 0; n < VD / 8; ++n) {
+                float* dst = mo + ((size_t)warp_n * 16 + row) * VD + n * 8 + tq * 2;
                 dst[0] = o[n][2 * i]; dst[1] = o[n][2 * i + 1];
             }
             if (tq == 0) {
@@ -340,8 +356,8 @@ flash_paged_kernel(const FlashParams p) {
             }
         }
         __syncthreads();
-        for (int idx = tid; idx < n_rows * HD; idx += NTHREADS) {
-            const int row = idx / HD, d = idx - row * HD;
+        for (int idx = tid; idx < n_rows * VD; idx += NTHREADS) {
+            const int row = idx / VD, d = idx - row * VD;
             float m_all = -INFINITY;
 #pragma unroll
             for (int w = 0; w < WARPS_N; ++w) m_all = fmaxf(m_all, mml[(w * 16 + row) * 2]);
@@ -351,16 +367,16 @@ flash_paged_kernel(const FlashParams p) {
             for (int w = 0; w < WARPS_N; ++w) {
                 const float f = exp2f(mml[(w * 16 + row) * 2] - m_s);
                 l_all += mml[(w * 16 + row) * 2 + 1] * f;
-                acc += mo[((size_t)w * 16 + row) * HD + d] * f;
+                acc += mo[((size_t)w * 16 + row) * VD + d] * f;
             }
             const int rr = row0 + row;
             const int t = rr / G;
             const size_t row_out = (size_t)(q_start + t) * p.nh + kvh * G + (rr - t * G);
             if (p.num_splits == 1) {
-                p.out[row_out * HD + d] = __float2bfloat16_rn(acc * flash_final(m_all, l_all, p.sinks, p.gate, row_out, kvh * G + (rr - t * G)));
+                p.out[row_out * VD + d] = __float2bfloat16_rn(acc * flash_final(m_all, l_all, p.sinks, p.gate, row_out, kvh * G + (rr - t * G)));
             } else {
                 const size_t prow = (size_t)split * p.n_tokens * p.nh + row_out;
-                p.part_o[prow * HD + d] = acc;
+                p.part_o[prow * VD + d] = acc;
                 if (d == 0) { p.part_ml[prow * 2] = m_all; p.part_ml[prow * 2 + 1] = l_all; }
             }
         }
@@ -373,15 +389,15 @@ flash_paged_kernel(const FlashParams p) {
         const size_t row_out = (size_t)tok[i] * p.nh + head[i];
         if (p.num_splits == 1) {
             const float inv = flash_final(m_run[i], l_run[i], p.sinks, p.gate, row_out, head[i]);
-            __nv_bfloat16* dst = p.out + row_out * HD + tq * 2;
+            __nv_bfloat16* dst = p.out + row_out * VD + tq * 2;
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n)
+            for (int n = 0; n < VD / 8; ++n)
                 *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
         } else {
             const size_t prow = (size_t)split * p.n_tokens * p.nh + row_out;
-            float* dst = p.part_o + prow * HD + tq * 2;
+            float* dst = p.part_o + prow * VD + tq * 2;
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n) { dst[n * 8] = o[n][2 * i]; dst[n * 8 + 1] = o[n][2 * i + 1]; }
+            for (int n = 0; n < VD / 8; ++n) { dst[n * 8] = o[n][2 * i]; dst[n * 8 + 1] = o[n][2 * i + 1]; }
             if (tq == 0) { p.part_ml[prow * 2] = m_run[i]; p.part_ml[prow * 2 + 1] = l_run[i]; }
         }
     }
@@ -402,7 +418,7 @@ __device__ __forceinline__ float merge_splits(const float* __restrict__ part_o, 
             const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + r);
             m[i] = have ? ml.x : -INFINITY;
             l[i] = have ? ml.y : 0.f;
-            o[i] = __ldcg(part_o + r * HEAD_DIM + d);
+            o[i] = __ldcg(part_o + r * V_DIM + d);
         }
         float m_new = m_run;
 #pragma unroll
@@ -438,7 +454,7 @@ __device__ __forceinline__ float4 merge_splits4(const float* __restrict__ part_o
             const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + r);
             m[i] = have ? ml.x : -INFINITY;
             l[i] = have ? ml.y : 0.f;
-            o[i] = __ldcg(reinterpret_cast<const float4*>(part_o + r * HEAD_DIM + d));
+            o[i] = __ldcg(reinterpret_cast<const float4*>(part_o + r * V_DIM + d));
         }
         float m_new = m_run;
 #pragma unroll
@@ -459,9 +475,9 @@ __device__ __forceinline__ float4 merge_splits4(const float* __restrict__ part_o
     return make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
 }
 
-// Merge the partial results of the key splits: HEAD_DIM / 4 threads per (token, head) row, four neighbouring
+// Merge the partial results of the key splits: V_DIM / 4 threads per (token, head) row, four neighbouring
 // elements each (16-byte reads of the partials, an 8-byte store); a block of 128 threads takes several rows.
-#define COMBINE_TPR (HEAD_DIM / 4)                 // threads per row
+#define COMBINE_TPR (V_DIM / 4)                    // threads per row
 #define COMBINE_ROWS (128 / COMBINE_TPR)           // rows per block
 __global__ void flash_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      __nv_bfloat16* __restrict__ out, int rows, int num_splits,
@@ -475,7 +491,7 @@ __global__ void flash_combine_kernel(const float* __restrict__ part_o, const flo
     uint2 o2;
     o2.x = pack_bf16(v.x, v.y);
     o2.y = pack_bf16(v.z, v.w);
-    *reinterpret_cast<uint2*>(out + (size_t)row * HEAD_DIM + d) = o2;
+    *reinterpret_cast<uint2*>(out + (size_t)row * V_DIM + d) = o2;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -494,7 +510,7 @@ __global__ void flash_combine_kernel(const float* __restrict__ part_o, const flo
 // for by the consumers, and after a wait that gave up (bounded, with a status word) the producer
 // waits, again bounded, for what it has requested - shared memory that a later CTA of the grid
 // inherits is never written by a copy of an earlier one.
-#if HEAD_DIM == 64 || HEAD_DIM == 128
+#if (HEAD_DIM == 64 || HEAD_DIM == 128) && RV_STANDARD_KV
 #define RV_HAVE_TMA_DECODE 1
 #include "tcgen05.cuh"
 #define TMA_HALVES (HEAD_DIM / 64)
@@ -1434,6 +1450,7 @@ RV_EXPORT int rv_flash_decode_balanced(const void* q, const void* cache, const i
                                        const int* ctx_lens, void* out, float* scratch, int* piece_count, int max_pieces,
                                        int n_tokens, int num_seqs, int nh, int nkv, int hd, int page_size, int max_blocks,
                                        float scale, int window, int ctas, cudaStream_t stream) {
+    if (!RV_STANDARD_KV) return RV_ERR_UNSUPPORTED;      // this kernel reads keys and values from two planes of one width
     if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
     if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 || max_pieces < 1)
         return RV_ERR_BAD_SIZE;
@@ -1472,8 +1489,8 @@ RV_EXPORT int rv_flash_decode_balanced(const void* q, const void* cache, const i
 
 template <int WARPS_M, int WARPS_N, int NSTAGES>
 static int launch_flash(const FlashParams& p, int num_seqs, cudaStream_t stream) {
-    const int merge_bytes = WARPS_N > 1 ? WARPS_N * 16 * (HEAD_DIM + 2) * 4 : 0;
-    const int smem = max(NSTAGES * 2 * TILE_BYTES, merge_bytes);
+    const int merge_bytes = WARPS_N > 1 ? WARPS_N * 16 * (V_DIM + 2) * 4 : 0;
+    const int smem = max(NSTAGES * STAGE_TILES * TILE_BYTES, merge_bytes);
     static RvPerDevice configured;
     if (int e = rv_configure_smem(configured, flash_paged_kernel<WARPS_M, WARPS_N, NSTAGES>, smem)) return e;
     const dim3 grid(p.row_tiles * p.num_splits, p.nkv, num_seqs);
@@ -1482,10 +1499,12 @@ static int launch_flash(const FlashParams& p, int num_seqs, cudaStream_t stream)
 }
 
 RV_EXPORT int rv_flash_head_dim() { return HEAD_DIM; }
+RV_EXPORT int rv_flash_value_dim() { return V_DIM; }
+RV_EXPORT int rv_flash_planes() { return KV_PLANES; }
 
 // How many floats of scratch `rv_flash_attention` needs for `num_splits` > 1.
 RV_EXPORT long long rv_flash_scratch_floats(int n_tokens, int nh, int num_splits) {
-    return num_splits > 1 ? (long long)num_splits * n_tokens * nh * (HEAD_DIM + 2) : 0;
+    return num_splits > 1 ? (long long)num_splits * n_tokens * nh * (V_DIM + 2) : 0;
 }
 
 // mode 0: prefill / mixed tiling (64 rows per CTA); mode 1: decode tiling (16 rows, warps split
@@ -1513,7 +1532,7 @@ RV_EXPORT int rv_flash_attention_ex(const void* q, const void* cache, const int*
     p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.ctx_lens = ctx_lens;
     p.out = (__nv_bfloat16*)out;
     p.part_o = scratch;
-    p.part_ml = scratch ? scratch + (size_t)num_splits * n_tokens * nh * HEAD_DIM : nullptr;
+    p.part_ml = scratch ? scratch + (size_t)num_splits * n_tokens * nh * V_DIM : nullptr;
     p.n_tokens = n_tokens; p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.max_blocks = max_blocks;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
@@ -1717,6 +1736,7 @@ RV_EXPORT int rv_flash_attention_static(const void* q, const void* cache, const 
                                         int num_seqs, int nh, int nkv, int hd, int page_size, int max_blocks,
                                         float scale, int window, int mode, int max_q_len, int num_splits,
                                         cudaStream_t stream, char* err, int err_len) {
+    if (!RV_STANDARD_KV) return RV_ERR_UNSUPPORTED;      // this kernel reads keys and values from two planes of one width
     if (err && err_len > 0) err[0] = 0;
     if (num_splits < 1 || n_tokens < 0 || nh <= 0) {
         static_fail(err, err_len, "rv_flash_attention_static: bad sizes (num_splits %d, n_tokens %d, num_heads %d)", num_splits, n_tokens, nh);

@@ -9,8 +9,9 @@
 //                    the absorbing product fills afterwards), sigmoid of the gate logits into a float array.
 //   head_linear      out[t, h, :] = W[h] x[t, h, :] for W [nh, N, K]: the per-head products that move a head's key
 //                    up-projection onto its query and apply its value up-projection to the attended latent.
-//                    x and out are given with row and head strides (slices of wider rows).  FFMA on the CUDA cores,
-//                    float accumulation in one fixed order over K that does not depend on the number of rows.
+//                    x and out are given with row and head strides (slices of wider rows).  bfloat16 operands with
+//                    aligned rows run on the tensor cores (mma.sync), everything else as FFMA on the CUDA cores;
+//                    float accumulation either way, in an order over K that does not depend on the number of rows.
 //
 // All arithmetic is float; storage is float or bfloat16 per argument.  Any sizes.
 #include "common.cuh"
@@ -157,12 +158,95 @@ head_linear_kernel(const void* __restrict__ x, int x_dtype, long long x_row, lon
     }
 }
 
+// ------------------------------------------------------------------ the same on the tensor cores (bfloat16 operands)
+// 64 rows x 64 features per CTA of four warps (16 rows each), K in slices of 32 through padded shared-memory tiles,
+// mma.sync m16n8k16 with float accumulators; needs K a multiple of 8 and 16-byte aligned rows of x and W.
+__device__ __forceinline__ void hl_ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void hl_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+#define HM_T 64
+#define HM_K 32
+#define HM_ROW (HM_K + 8)      // elements of a shared-memory row: 80 bytes, an odd multiple of 16
+
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_row, long long x_head, const __nv_bfloat16* __restrict__ w,
+                       void* __restrict__ out, int out_dtype, long long o_row, long long o_head, int T, int N, int K) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    __shared__ __align__(16) __nv_bfloat16 xs[HM_T][HM_ROW];
+    __shared__ __align__(16) __nv_bfloat16 ws[HM_T][HM_ROW];
+    const int h = blockIdx.z, m0 = blockIdx.y * HM_T, n0 = blockIdx.x * HM_T;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const __nv_bfloat16* xb = x + (size_t)h * x_head;
+    const __nv_bfloat16* wb = w + (size_t)h * N * K;
+    float acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+    for (int k0 = 0; k0 < K; k0 += HM_K) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int idx = threadIdx.x + r * 128;
+            const int row = idx >> 2, c = (idx & 3) * 8;
+            uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+            if (k0 + c < K) {
+                if (m0 + row < T) a = *reinterpret_cast<const uint4*>(xb + (size_t)(m0 + row) * x_row + k0 + c);
+                if (n0 + row < N) b = *reinterpret_cast<const uint4*>(wb + (size_t)(n0 + row) * K + k0 + c);
+            }
+            *reinterpret_cast<uint4*>(&xs[row][c]) = a;
+            *reinterpret_cast<uint4*>(&ws[row][c]) = b;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HM_K / 16; ++kk) {
+            uint32_t a[4];
+            hl_ldmatrix_x4(a, &xs[warp * 16 + (lane & 15)][kk * 16 + (lane >> 4) * 8]);
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                uint32_t b[4];
+                hl_ldmatrix_x4(b, &ws[n2 * 16 + (lane >> 4) * 8 + (lane & 7)][kk * 16 + ((lane >> 3) & 1) * 8]);
+                hl_mma(acc[2 * n2], a, b[0], b[1]);
+                hl_mma(acc[2 * n2 + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    const int quad = lane >> 2, tq = lane & 3;
+    const size_t ob = (size_t)h * o_head;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = m0 + warp * 16 + quad + 8 * i;
+        if (m >= T) continue;
+#pragma unroll
+        for (int n8 = 0; n8 < 8; ++n8) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int n = n0 + n8 * 8 + tq * 2 + j;
+                if (n < N) lt_store(out, out_dtype, ob + (size_t)m * o_row + n, acc[n8][2 * i + j]);
+            }
+        }
+    }
+}
+
 RV_EXPORT int rv_head_linear(const void* x, int x_dtype, long long x_row, long long x_head, const void* w, int w_dtype,
                              void* out, int out_dtype, long long o_row, long long o_head, int T, int nh, int N, int K,
                              cudaStream_t stream) {
     if (T < 0 || nh <= 0 || N <= 0 || K <= 0 || nh > 65535) return RV_ERR_BAD_SIZE;
     if ((x_dtype | w_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
     if (T == 0) return RV_OK;
+    if (x_dtype == RV_DTYPE_BF16 && w_dtype == RV_DTYPE_BF16 && K % 8 == 0 && x_row % 8 == 0 && x_head % 8 == 0 &&
+        reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 && (T + HM_T - 1) / HM_T <= 65535) {
+        const dim3 g((N + HM_T - 1) / HM_T, (T + HM_T - 1) / HM_T, nh);
+        RV_LAUNCH_ST = rv_launch(head_linear_mma_kernel, dim3(g), dim3(128), 0, stream, (const __nv_bfloat16*)x, x_row, x_head,
+                                 (const __nv_bfloat16*)w, out, out_dtype, o_row, o_head, T, N, K);
+        return rv_launch_status();
+    }
     const dim3 grid((N + HL_TN - 1) / HL_TN, (T + HL_TM - 1) / HL_TM, nh);
     if (grid.y > 65535) return RV_ERR_BAD_SIZE;
     RV_LAUNCH_ST = rv_launch(head_linear_kernel, dim3(grid), dim3(256), 0, stream, x, x_dtype, x_row, x_head, w, w_dtype, out, out_dtype,

@@ -94,6 +94,7 @@ class CudaKernels:
     TMA_DECODE_EARLY = True   # ... and keys older than the step's own are requested before the wait for the kernel before
     BALANCED_DECODE = True  # decode attention by the kernel that cuts all tiles evenly over resident CTAs ...
     BALANCED_MIN_PAIRS = 256  # ... from this many (sequence, kv head) pairs on
+    LATENT_FLASH = True       # latent attention in bfloat16 runs on the tensor-core flash kernel where its sizes allow (else the plain kernel)
     FUSED_QKV_PREFILL = True  # from TCGEN05_MIN_ROWS rows on the prefill GEMM rotates and writes the cache in its epilogue
     FUSED_NORM_MAX_ROWS = 0 # rows up to which an RMSNorm is applied inside the decode GEMM that consumes it
     FUSED_QKV_MAX_ROWS = 64 # rows up to which q/k/v product, rotation and cache write are one kernel
@@ -411,13 +412,19 @@ class CudaKernels:
         return out
 
     def flash_attention(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window,
-                        mode=0, num_splits=1, q_filter=0, max_q_len=None, softcap=None, sinks=None, gate=None):
-        _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
-        lib = self._lib("attention_flash.cu", (f"-DHEAD_DIM={head_dim}",))
+                        mode=0, num_splits=1, q_filter=0, max_q_len=None, softcap=None, sinks=None, gate=None, value_dim=None):
+        """The mma.sync flash kernel (mode 0: 64 rows per CTA, prompt portions; mode 1: 16 rows, warps and CTAs split the keys).
+        `value_dim`: the build for one-plane caches, whose rows are keys in full and values in their leading `value_dim`
+        elements; `out` then has rows of that width."""
+        _need(q, "q", torch.bfloat16); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
+        defines = (f"-DHEAD_DIM={head_dim}",) if value_dim is None else (f"-DHEAD_DIM={head_dim}", f"-DV_DIM={value_dim}", "-DKV_PLANES=1")
+        if cache_layer.shape[1] != (2 if value_dim is None else 1):
+            raise KernelError(f"flash_attention: a cache layer of {cache_layer.shape[1]} planes for a kernel of {2 if value_dim is None else 1}")
+        lib = self._lib("attention_flash.cu", defines)
         T = q.shape[0]
         scratch = None
         if num_splits > 1:
-            scratch = torch.empty((num_splits * T * num_heads * (head_dim + 2),), dtype=torch.float32, device=q.device)
+            scratch = torch.empty((num_splits * T * num_heads * ((value_dim or head_dim) + 2),), dtype=torch.float32, device=q.device)
         st = lib.rv_flash_attention_ex(
             _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens),
             _ptr(out), _ptr(scratch), c_int(T), c_int(meta.num_seqs), c_int(num_heads), c_int(num_kv_heads),
@@ -425,6 +432,8 @@ class CudaKernels:
             c_int(mode), c_int(max_q_len or meta.max_q_len), c_int(num_splits), c_int(q_filter), c_float(softcap or 0.0),
             _ptr(sinks), _ptr(gate), self._stream())
         _check("flash_attention", st)
+        if num_splits > 1:
+            COUNTERS['launches'] += 1
         return out
 
     def attention_tcgen05(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, status=None,
@@ -1100,6 +1109,19 @@ class CudaKernels:
             raise KernelError(f"latent_attention: a value of {value_dim} out of a row of {row}")
         self._check_attention_extras(q_row.view(T, -1), num_heads, None, gate)
         out = torch.empty((T, num_heads, value_dim), dtype=q_row.dtype, device=q_row.device)
+        page = cache_layer.shape[3]
+        if self.LATENT_FLASH and q_row.dtype == torch.bfloat16 and row % 16 == 0 and value_dim % 16 == 0 and row <= 256 \
+                and not (page & (page - 1)):
+            # the tensor-core kernel: all heads of a token are rows of one tile over the token's single "kv head"
+            args = (q_row, cache_layer, meta, out, num_heads, 1, row, scale, None)
+            if meta.max_q_len == 1:
+                self.flash_attention(*args, mode=1, num_splits=self.decode_splits(meta, num_heads, 1), gate=gate, value_dim=value_dim)
+            elif meta.num_decode == 0:
+                self.flash_attention(*args, mode=0, gate=gate, value_dim=value_dim)
+            else:
+                self.flash_attention(*args, mode=0, q_filter=2, gate=gate, value_dim=value_dim)
+                self.flash_attention(*args, mode=1, q_filter=1, max_q_len=1, gate=gate, value_dim=value_dim)
+            return out
         st = self._lib("attention_ref.cu").rv_paged_attention_ref_ex(
             _ptr(q_row), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens),
             _ptr(meta.token_seq), _ptr(out), c_int(T), c_int(num_heads), c_int(1), c_int(row), c_int(cache_layer.shape[3]),

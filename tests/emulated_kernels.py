@@ -27,12 +27,104 @@ class EmulatedKernels:
         r = 1.0 / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps)
         return (xf * r * gamma.float()).to(out_dtype or x.dtype)
 
-    def residual_rmsnorm(self, y, gamma, eps, residual, rounded_dtype=None, keep_residual=True):
+    def residual_rmsnorm(self, y, gamma, eps, residual, rounded_dtype=None, keep_residual=True, next_norm=None):
         r = self.rmsnorm(y.float(), gamma, eps)
         if residual is not None:
             residual += r
             r = residual
+        if next_norm is not None:
+            return r, self.rmsnorm(r, *next_norm).to(rounded_dtype)
         return (r if keep_residual else None), (r.to(rounded_dtype) if rounded_dtype is not None else None)
+
+    def stream_add(self, x, emb, table, index):
+        x += table[index].float()
+        if emb is not None:
+            x += emb
+        return x
+
+    def polynorm(self, z, coef, eps, out_dtype=None):
+        zf = z.float()
+        n = lambda v: v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+        return (coef[0] * n(zf) + coef[1] * n(zf * zf) + coef[2] * n(zf * zf * zf) + coef[3]).to(out_dtype or z.dtype)
+
+    def softcap(self, logits, cap):
+        logits.copy_(cap * torch.tanh(logits / cap))
+        return logits
+
+    def latent_prepare(self, proj, c_gamma, eps, positions, cos, sin, slot_mapping, cache_layer, num_heads, head_dim, rot_dim,
+                       kv_rank, out_dtype, with_gate=True, write_kv=True):
+        T, row = proj.shape[0], kv_rank + rot_dim
+        x = proj.float()
+        qw = num_heads * (head_dim + rot_dim)
+        pos = positions.long()
+
+        def turn(v):          # [..., rot_dim]: pairs (2i, 2i + 1) below the tables' width
+            if cos is None:
+                return v
+            half = cos.shape[1]
+            c, s = cos[pos], sin[pos]
+            while c.dim() < v.dim():
+                c, s = c.unsqueeze(1), s.unsqueeze(1)
+            out = v.clone()
+            a, b = v[..., 0:2 * half:2], v[..., 1:2 * half:2]
+            out[..., 0:2 * half:2] = a * c - b * s
+            out[..., 1:2 * half:2] = b * c + a * s
+            return out
+
+        q = x[:, :qw].view(T, num_heads, head_dim + rot_dim)
+        q_plain = q[:, :, :head_dim].contiguous().to(out_dtype)
+        q_row = torch.zeros((T, num_heads, row), dtype=out_dtype)
+        q_row[:, :, kv_rank:] = turn(q[:, :, head_dim:]).to(out_dtype)
+        if write_kv:
+            c = self.rmsnorm(x[:, qw:qw + kv_rank], c_gamma, eps)
+            line = torch.cat([c, turn(x[:, qw + kv_rank:qw + row])], dim=1).to(out_dtype)
+            ps = cache_layer.shape[3]
+            for t in range(T):
+                slot = int(slot_mapping[t])
+                if slot >= 0:
+                    cache_layer[slot // ps, 0, 0, slot % ps, :] = line[t]
+        gate = torch.sigmoid(x[:, qw + row:qw + row + num_heads]) if with_gate else None
+        return q_plain, q_row, gate
+
+    def head_linear(self, x, weight, out=None, out_dtype=None):
+        y = torch.einsum("thk,hnk->thn", x.float(), weight.float()).contiguous()
+        if out is None:
+            return y.to(out_dtype or x.dtype)
+        out.copy_(y.to(out.dtype))
+        return out
+
+    def latent_attention(self, q_row, cache_layer, meta, num_heads, row, value_dim, scale, gate=None):
+        T = q_row.shape[0]
+        ps = cache_layer.shape[3]
+        out = torch.zeros((T, num_heads, value_dim), dtype=q_row.dtype)
+        cu = meta.cu_seqlens.tolist()
+        for s in range(meta.num_seqs):
+            ctx = int(meta.ctx_lens[s])
+            if ctx <= 0:
+                continue
+            q_len = cu[s + 1] - cu[s]
+            table = meta.block_tables[s].tolist()
+            for i in range(q_len):
+                t, pos = cu[s] + i, ctx - q_len + i
+                pages = [table[j // ps] for j in range(pos + 1)]
+                assert all(p >= 0 for p in pages), "attention reads a page that was given back"
+                rows = cache_layer[pages, 0, 0, [j % ps for j in range(pos + 1)], :].float()
+                p = torch.softmax((q_row[t].float() @ rows.T) * scale, -1)          # [heads, keys]
+                o = p @ rows[:, :value_dim]
+                if gate is not None:
+                    o = o * gate[t][:, None]
+                out[t] = o.to(q_row.dtype)
+        return out
+
+    def moe_experts(self, x, chosen, gate_up, down, weight, add=None, out_dtype=None):
+        T, ff = x.shape[0], gate_up.shape[1] // 2
+        out = torch.zeros((T, x.shape[1])) if add is None else add.clone().float()
+        for t in range(T):
+            for e in chosen[t].tolist():
+                gu = gate_up[e].float() @ x[t].float()
+                g, u = gu[:ff], gu[ff:]
+                out[t] += weight * (down[e].float() @ (g / (1.0 + torch.exp(-g)) * u).to(x.dtype).float())
+        return out.to(out_dtype or x.dtype)
 
     def act_mul(self, gate_up, activation, out_dtype=None):
         inter = gate_up.shape[1] // 2
