@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200: decode tokens per second, prefill, roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape NAME]
-                    [--workload decode|serve|tufirax] [--impl ours|reference]
+                    [--workload decode|serve|tufirax|vipelix] [--impl ours|reference]
 
 The default run has the layer sizes of Llama-3.1-8B (32 layers, hidden 4096, 32 query heads,
 8 key/value heads of 128, MLP 14336, vocabulary 128256, llama3 rotary scaling) with random
@@ -566,6 +566,224 @@ def run_tufirax(args):
     print(json.dumps(out))
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --workload vipelix: the Vipelix design (latent attention over one cached row per token, a norm in front of and behind
+# every sublayer around a float32 stream, a dense feed-forward with a PolyNorm activation, experts chosen by a table
+# lookup plus a shared expert, a span of layers that runs twice) at layer sizes that resemble real models, beside the
+# Llama decoder of this engine at the same width, heads and depth whose feed-forward is as wide as what a token of
+# the mixture activates; then each of the design's own kernels alone beside the like kernel of the Llama path, with
+# its bytes or FLOPs over its time against the measured copy bandwidth or bf16 peak.  Random weights; its own JSON line.
+VIPELIX_SIZES = {
+    "2k": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=192, ff=8192, e_ff=1408, experts=16, top=2, shared=2816, layers=4, times=2),
+    "4k": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, rank=192, ff=14336, e_ff=2048, experts=32, top=4, shared=4096, layers=4, times=2),
+}
+
+
+def vipelix_pair(size: dict, vocab: int = 32768):
+    """(Vipelix configuration, Llama configuration).  The Vipelix stack: a dense layer, then layers of experts; all of
+    them run `times` times.  The Llama stack has as many layers as the Vipelix one has layer runs."""
+    mixer = {"heads": size["heads"], "dim": size["dim"], "rot_dim": size["rot"], "vdim": size["vdim"], "kv_rank": size["rank"],
+             "scale": (size["dim"] + size["rot"]) ** -0.5, "rot": {"dims": size["rot"], "base": 500000.0}}
+    dense = {"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": size["ff"]}}
+    moe = {"type": "latent_attention", "mixer": mixer,
+           "mlp": {"kind": "moe", "expert": {"ff": size["e_ff"]}, "router": {"experts": size["experts"], "top": size["top"]},
+                   "shared": {"ff": size["shared"]}}}
+    vip = {"architecture": "Vipelix", "width": size["width"], "vocab": vocab, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+           "loop": {"start": 0, "stop": size["layers"], "times": size["times"]},
+           "layers": [dense] + [moe] * (size["layers"] - 1)}
+    llama = {"architectures": ["LlamaForCausalLM"], "hidden_size": size["width"], "num_hidden_layers": size["layers"] * size["times"],
+             "num_attention_heads": size["heads"], "num_key_value_heads": size["heads"] // 4, "head_dim": size["dim"],
+             "intermediate_size": size["top"] * size["e_ff"] + size["shared"], "vocab_size": vocab, "max_position_embeddings": 8192,
+             "rms_norm_eps": 1e-6, "rope_theta": 500000.0, "tie_word_embeddings": True, "hidden_act": "silu", "torch_dtype": "bfloat16"}
+    return vip, llama
+
+
+def run_vipelix(args):
+    import torch
+
+    from rvllm_b200 import LLM, config_from_dict
+    from rvllm_b200.engine import StepEntry
+    from rvllm_b200.kernels import AttentionMeta
+
+    peaks = measured_peaks()
+    PROMPT, CTX, batch = 2048, 4096, args.batch
+    gen = torch.Generator().manual_seed(0)
+    out = {"workload": "vipelix", "dtype": "bf16", "data": "synthetic", "peaks": peaks["source"], "prompt_len": PROMPT, "batch": batch,
+           "steps": args.steps, "warmup": args.warmup, "models": {}, "kernels": {}}
+
+    def measure(cfg_dict):
+        config = config_from_dict(cfg_dict)
+        llm = LLM(config=config, random_weights=True, seed=0, dtype="bfloat16", block_size=16, num_blocks=batch * (CTX // 16) + 8,
+                  max_model_len=CTX, max_num_seqs=batch, max_num_batched_tokens=PROMPT, enforce_eager=args.eager)
+        runner, V = llm.engine.runner, llm.engine.spec.vocab_size
+        p = torch.randint(0, V, (PROMPT,), generator=gen).tolist()
+        for _ in range(3):
+            runner.step([StepEntry("w", p, [PROMPT - 1])])
+            runner.finish("w")
+        torch.cuda.synchronize()
+        pf = []
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            runner.step([StepEntry("p", p, [PROMPT - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            runner.finish("p")
+            pf.append(a.elapsed_time(b))
+        ids = [f"d{i}" for i in range(batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, torch.randint(0, V, (PROMPT,), generator=gen).tolist(), [])])
+        for _ in range(args.warmup):
+            runner.step([StepEntry(r, [1], [0]) for r in ids])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            runner.step([StepEntry(r, [1], [0]) for r in ids])
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        for rid in ids:
+            runner.finish(rid)
+        kernels = llm.engine.kernels
+        kernels.raise_on_abort()
+        del llm
+        torch.cuda.empty_cache()
+        return {"prefill_ms": round(min(pf), 3), "prefill_tok_s": round(PROMPT / (min(pf) / 1e3), 1),
+                "decode_ms_per_step": round(ms, 4), "decode_tok_s": round(batch / (ms / 1e3), 1)}, kernels
+
+    K = None
+    for name in (args.sizes.split(",") if args.sizes else list(VIPELIX_SIZES)):
+        vip, llama = vipelix_pair(VIPELIX_SIZES[name])
+        a, K = measure(vip)
+        b, K = measure(llama)
+        out["models"][name] = {"vipelix": a, "llama_same_size": b, "layer_runs": VIPELIX_SIZES[name]["layers"] * VIPELIX_SIZES[name]["times"],
+                               "prefill_ratio": round(a["prefill_tok_s"] / b["prefill_tok_s"], 3),
+                               "decode_ratio": round(a["decode_tok_s"] / b["decode_tok_s"], 3)}
+
+    # ---- the design's kernels alone, at the "4k" sizes, beside the like kernel of the Llama path ------------------
+    z = VIPELIX_SIZES["4k"]
+    dev, bf = "cuda", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bw, peak = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+
+    def by_bytes(name, ms, nbytes, like=None):
+        out["kernels"][name] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / (ms / 1e3) / bw, 3)}
+        if like is not None:
+            out["kernels"][name]["like"] = like
+
+    def by_flops(name, ms, flops, like=None):
+        out["kernels"][name] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "frac_bf16": round(flops / (ms / 1e3) / peak, 3)}
+        if like is not None:
+            out["kernels"][name]["like"] = like
+
+    T, W, FF = PROMPT, z["width"], z["ff"]
+    H, D, RD, V, R = z["heads"], z["dim"], z["rot"], z["vdim"], z["rank"]
+    ROW = R + RD
+    y, res = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev)
+    g = torch.ones(W, dtype=bf, device=dev)
+    xb = torch.randn(T, W, device=dev).to(bf)
+    ms_like = _time_kernel(lambda: K.rmsnorm(xb, g, 1e-6), flush=flush)
+    like = {"kernel": "rmsnorm", "ms": round(ms_like, 4), "frac_hbm": round(T * W * 4 / (ms_like / 1e3) / bw, 3)}
+    by_bytes("residual_rmsnorm_then_norm", _time_kernel(lambda: K.residual_rmsnorm(y, g, 1e-6, res, bf, next_norm=(g, 1e-6)), flush=flush),
+             T * W * (4 + 4 + 4 + 2), like)
+    zf = torch.randn(T, FF, device=dev)
+    gub = torch.randn(T, 2 * FF, device=dev).to(bf)
+    ms_like = _time_kernel(lambda: K.silu_mul(gub), flush=flush)
+    like = {"kernel": "silu_mul", "ms": round(ms_like, 4), "frac_hbm": round(T * FF * 6 / (ms_like / 1e3) / bw, 3)}
+    coef = torch.tensor([0.5, 0.3, 0.2, 0.1], device=dev)
+    by_bytes("polynorm", _time_kernel(lambda: K.polynorm(zf, coef, 1e-6, bf), flush=flush), T * FF * (4 + 2), like)
+
+    # what follows the stacked projection: the latent's norm, the rotations, the cache row, the split of q, the gate
+    pages = PROMPT // 16
+    cache1 = torch.zeros(pages, 1, 1, 16, ROW, dtype=bf, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * torch.tensor([500000.0 ** (-2.0 * i / RD) for i in range(RD // 2)], dtype=torch.float64)[None, :]
+    cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+    proj = torch.randn(T, H * (D + RD) + ROW + H, device=dev)
+    gamma = torch.ones(R, dtype=bf, device=dev)
+    nkv = H // 4
+    cache2 = torch.zeros(pages, 2, nkv, 16, D, dtype=bf, device=dev)
+    ang2 = torch.arange(T, dtype=torch.float64)[:, None] * torch.tensor([500000.0 ** (-2.0 * i / D) for i in range(D // 2)], dtype=torch.float64)[None, :]
+    cos2, sin2 = torch.cos(ang2).float().to(dev), torch.sin(ang2).float().to(dev)
+    proj_qkv = torch.randn(T, (H + 2 * nkv) * D, device=dev)
+    ms_like = _time_kernel(lambda: K.rope_cache_write(proj_qkv, None, pos, cos2, sin2, pos, cache2, H, nkv, D, out_dtype=bf), flush=flush)
+    like = {"kernel": "rope_cache_write", "ms": round(ms_like, 4), "frac_hbm": round(T * (H + 2 * nkv) * D * 6 / (ms_like / 1e3) / bw, 3)}
+    by_bytes("latent_prepare", _time_kernel(lambda: K.latent_prepare(proj, gamma, 1e-6, pos, cos, sin, pos, cache1, H, D, RD, R, bf), flush=flush),
+             T * (proj.shape[1] * 4 + (H * (D + RD) + ROW) * 2 + H * 4), like)
+
+    # the per-head products (the key up-projection moved onto the query; the value up-projection of the attended latent)
+    q_plain, q_row = torch.randn(T, H, D, device=dev).to(bf), torch.zeros(T, H, ROW, dtype=bf, device=dev)
+    uk_t, uv = torch.randn(H, R, D, device=dev).to(bf), torch.randn(H, V, R, device=dev).to(bf)
+    wl = torch.randn(H * R, W, device=dev).to(bf)
+    ms_like = _time_kernel(lambda: K.linear(xb, wl), flush=flush)
+    like = {"kernel": "linear (tcgen05), 2,048 x %d x %d" % (H * R, W), "ms": round(ms_like, 4),
+            "frac_bf16": round(2.0 * T * H * R * W / (ms_like / 1e3) / peak, 3)}
+    by_flops("head_linear_absorb", _time_kernel(lambda: K.head_linear(q_plain, uk_t, q_row[:, :, :R]), flush=flush), 2.0 * T * H * R * D, like)
+    o_lat = torch.randn(T, H, R, device=dev).to(bf)
+    by_flops("head_linear_values", _time_kernel(lambda: K.head_linear(o_lat, uv, None), flush=flush), 2.0 * T * H * R * V)
+
+    def latent_case(q_len, ctx, seqs):
+        n = seqs * (ctx // 16)
+        cache = torch.randn(n, 1, 1, 16, ROW, device=dev).to(bf)
+        tables = torch.arange(n, dtype=torch.int32, device=dev).view(seqs, ctx // 16)
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        meta = AttentionMeta(tables, cu, torch.full((seqs,), ctx, dtype=torch.int32, device=dev),
+                             torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len), None, seqs, q_len, ctx, 16,
+                             seqs if q_len == 1 else 0)
+        return torch.randn(seqs * q_len, H, ROW, device=dev).to(bf), cache, meta, torch.rand(seqs * q_len, H, device=dev)
+
+    def llama_case(q_len, ctx, seqs):
+        n = seqs * (ctx // 16)
+        cache = torch.randn(n, 2, nkv, 16, D, device=dev).to(bf)
+        tables = torch.arange(n, dtype=torch.int32, device=dev).view(seqs, ctx // 16)
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        meta = AttentionMeta(tables, cu, torch.full((seqs,), ctx, dtype=torch.int32, device=dev),
+                             torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len), None, seqs, q_len, ctx, 16,
+                             seqs if q_len == 1 else 0)
+        return torch.randn(seqs * q_len, H * D, device=dev).to(bf), cache, meta
+
+    q, cache, meta, gate = latent_case(PROMPT, PROMPT, 1)
+    ql, cl, ml = llama_case(PROMPT, PROMPT, 1)
+    ms_like = _time_kernel(lambda: K.paged_attention(ql, cl, ml, H, nkv, D, D ** -0.5, None), flush=flush)
+    like = {"kernel": "attention_prefill (tcgen05, heads of %d)" % D, "ms": round(ms_like, 4),
+            "frac_bf16": round(4.0 * H * D * PROMPT * PROMPT / 2 / (ms_like / 1e3) / peak, 3)}
+    by_flops("latent_attention_prefill", _time_kernel(lambda: K.latent_attention(q, cache, meta, H, ROW, R, 0.07, gate=gate), flush=flush),
+             2.0 * H * (ROW + R) * PROMPT * PROMPT / 2, like)
+    q, cache, meta, gate = latent_case(1, PROMPT, batch)
+    ql, cl, ml = llama_case(1, PROMPT, batch)
+    ms_like = _time_kernel(lambda: K.paged_attention(ql, cl, ml, H, nkv, D, D ** -0.5, None), flush=flush)
+    like = {"kernel": "attention_decode", "ms": round(ms_like, 4), "frac_hbm": round(batch * PROMPT * 2 * nkv * D * 2 / (ms_like / 1e3) / bw, 3)}
+    by_bytes("latent_attention_decode", _time_kernel(lambda: K.latent_attention(q, cache, meta, H, ROW, R, 0.07, gate=gate), flush=flush),
+             batch * PROMPT * ROW * 2, like)
+
+    # the experts: a prompt's tokens sorted by expert through the grouped products, and a decode step's through the streaming kernels
+    E, top, EF = z["experts"], z["top"], z["e_ff"]
+    gate_up, down = torch.randn(E, 2 * EF, W, device=dev).to(bf) * 0.02, torch.randn(E, W, EF, device=dev).to(bf) * 0.02
+    table = torch.rand(32768, E, device=dev).argsort(1)[:, :top].to(torch.int32).contiguous()
+    tokens = torch.randint(0, 32768, (T,), device=dev, dtype=torch.int32)
+    chosen = K.gather_rows(table, tokens)
+    wgu = torch.randn(2 * top * EF, W, device=dev).to(bf) * 0.02
+    wd = torch.randn(W, top * EF, device=dev).to(bf) * 0.02
+    ms_like = _time_kernel(lambda: K.linear(K.gate_up_silu(xb, wgu), wd, out_dtype=torch.float32), flush=flush)
+    flops = 6.0 * T * top * EF * W
+    like = {"kernel": "gated MLP as wide as the chosen experts (two tcgen05 products)", "ms": round(ms_like, 4),
+            "frac_bf16": round(flops / (ms_like / 1e3) / peak, 3)}
+    by_flops("moe_experts_prefill", _time_kernel(lambda: K.moe_experts(xb, chosen, gate_up, down, 1.0 / top, out_dtype=torch.float32), flush=flush),
+             flops, like)
+    xd = xb[:batch].contiguous()
+    cd = chosen[:batch].contiguous()
+    touched = len(set(cd.flatten().tolist()))
+    ms_like = _time_kernel(lambda: K.linear(K.gate_up_silu(xd, wgu), wd, out_dtype=torch.float32), flush=flush)
+    like = {"kernel": "gated MLP as wide as the chosen experts (decode GEMMs)", "ms": round(ms_like, 4),
+            "frac_hbm": round(3 * top * EF * W * 2 / (ms_like / 1e3) / bw, 3)}
+    by_bytes("moe_experts_decode", _time_kernel(lambda: K.moe_experts(xd, cd, gate_up, down, 1.0 / top, out_dtype=torch.float32), flush=flush),
+             touched * 3 * EF * W * 2, like)
+    out["kernels"]["moe_experts_decode"]["experts_touched"] = touched
+    K.raise_on_abort()
+    print(json.dumps(out))
+
+
 def run_serve(args):
     print(json.dumps(serve_workload(args.shape, args.layers, args.requests, args.output_len, args.budget, args.eager)))
 
@@ -578,10 +796,10 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES), help="layer sizes of the model")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "tufirax"],
-                    help="decode: the benchmark's one JSON line; serve: continuous batching of uneven prompts; tufirax: the Tufirax "
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "tufirax", "vipelix"],
+                    help="decode: the benchmark's one JSON line; serve: continuous batching of uneven prompts; tufirax, vipelix: that "
                          "design at real layer sizes beside the Llama decoder of equal size, and its kernels alone")
-    ap.add_argument("--sizes", default="", help="tufirax: which sizes to run, with commas (default: all)")
+    ap.add_argument("--sizes", default="", help="tufirax, vipelix: which sizes to run, with commas (default: all)")
     ap.add_argument("--requests", type=int, default=64, help="serve: number of requests")
     ap.add_argument("--output-len", type=int, default=256, help="serve: tokens generated per request")
     ap.add_argument("--budget", type=int, default=2048, help="serve: tokens per step")
@@ -601,6 +819,8 @@ def main():
     ensure_built()
     if args.workload == "tufirax":
         run_tufirax(args)
+    elif args.workload == "vipelix":
+        run_vipelix(args)
     elif args.workload == "serve":
         run_serve(args)
     else:

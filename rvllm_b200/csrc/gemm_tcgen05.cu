@@ -96,6 +96,11 @@ struct GemmParams {
     const float* sin_t;
     int nh, nkv, hd, page_size, table_rows;
     int act;                       // EPI_GATED: 0 SiLU, 1 the tanh form of GELU
+    // Grouped product (plain and gated epilogues, the build on single CTAs): W holds `groups` matrices of N rows one
+    // below the other, and row tile t of x (TILE_ROWS rows) is multiplied with matrix tile_group[t]; a negative entry
+    // marks a row tile that nobody uses, which every role of the kernel skips.  The rows of x are sorted by group
+    // and every group's rows padded to whole tiles by the caller (the experts of a mixture).
+    const int* tile_group;         // [m_tiles] or nullptr
 };
 
 
@@ -281,6 +286,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
                 const int m0 = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM;      // this CTA's 128 rows
                 const int nt = tile / p.m_tiles;
+                const int grp = p.tile_group ? __ldg(p.tile_group + tile % p.m_tiles) : 0;
+                if (grp < 0) continue;                                              // a row tile without rows
+                const int w_base = grp * p.N;                                       // the group's first row of W
                 for (int kb = kb_first; kb < kb_last; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, &abort_flag, 1)) { ok = false; break; }
                     const uint32_t a_dst = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
@@ -289,7 +297,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         // this CTA's 128 of the tile's 256 weight rows (gated: the first CTA has the gate
                         // rows, the second the up rows of the same output columns); the first CTA's
                         // barrier counts both CTAs' bytes
-                        const int w0 = gated ? (rank == 0 ? nt * (BN / 2) : half_n + nt * (BN / 2)) : nt * BN + (int)rank * (BN / 2);
+                        const int w0 = w_base + (gated ? (rank == 0 ? nt * (BN / 2) : half_n + nt * (BN / 2)) : nt * BN + (int)rank * (BN / 2));
                         const uint32_t bar = pair_map(full0 + 8 * stage, 0);
                         if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * STAGE_BYTES);
                         tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, bar);
@@ -302,11 +310,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     mbar_expect_tx(bar, STAGE_BYTES);
                     tma_load_2d(a_dst, &map_a, kb * BK, m0, bar);
                     if (gated) {       // 128 gate rows, then the 128 up rows of the same columns
-                        tma_load_2d(b_dst, &map_b, kb * BK, nt * (BN / 2), bar);
-                        tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, kb * BK, half_n + nt * (BN / 2), bar);
+                        tma_load_2d(b_dst, &map_b, kb * BK, w_base + nt * (BN / 2), bar);
+                        tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, kb * BK, w_base + half_n + nt * (BN / 2), bar);
                     } else {
-                        tma_load_2d(b_dst, &map_b, kb * BK, nt * BN, bar);
-                        tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, kb * BK, nt * BN + BN / 2, bar);
+                        tma_load_2d(b_dst, &map_b, kb * BK, w_base + nt * BN, bar);
+                        tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, kb * BK, w_base + nt * BN + BN / 2, bar);
                     }
                     ++issued;
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -335,6 +343,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int local = 0;
             bool ok = true;
             for (int tile = worker; tile < num_tiles && ok; tile += num_workers, ++local) {
+                if (p.tile_group && __ldg(p.tile_group + tile % p.m_tiles) < 0) { --local; continue; }   // (skipped by every role)
                 const int buf = local & 1;
                 const uint32_t use = (uint32_t)(local >> 1);
                 if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_flag, 2)) { ok = false; break; }
@@ -363,6 +372,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int local = 0;
         bool ok = true;
         for (int tile = worker; tile < num_tiles && ok; tile += num_workers, ++local) {
+            if (p.tile_group && __ldg(p.tile_group + tile % p.m_tiles) < 0) { --local; continue; }
             const int buf = local & 1;
             const uint32_t use = (uint32_t)(local >> 1);
             if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_flag, 4)) {
@@ -650,6 +660,34 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
     // N/2 read up rows, whose products the epilogue never stores
     p.n_tiles = epilogue == EPI_GATED ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
     return launch_gemm(map_a, map_b, p, max_ctas, stream);
+}
+
+// The grouped product: x [M, K] with M a multiple of the row tile, rows sorted by group and padded per group;
+// w [groups * N, K]; tile_group [M / row tile] on the device (negative: tile unused); out [M, N] (gated: N / 2 columns).
+// epilogue 0 (plain) or 2 (gated, SiLU).  The build on single CTAs only (row tiles of 128).
+RV_EXPORT int rv_gemm_tcgen05_row_tile() { return TILE_ROWS; }
+
+RV_EXPORT int rv_gemm_tcgen05_grouped(const void* x, const void* w, const int* tile_group, void* out, int out_f32,
+                                      int M, int N, int K, int groups, int epilogue, int* status, cudaStream_t stream) {
+    if (RV_PAIR) return RV_ERR_UNSUPPORTED;
+    if (M < 0 || N <= 0 || K <= 0 || groups <= 0 || !tile_group) return RV_ERR_BAD_SIZE;
+    if (epilogue != EPI_PLAIN && epilogue != EPI_GATED) return RV_ERR_UNSUPPORTED;
+    if (K % 8 || M % TILE_ROWS) return RV_ERR_UNSUPPORTED;
+    if (epilogue == EPI_GATED && (N & 1)) return RV_ERR_BAD_SIZE;
+    if ((long long)groups * N > 0x7fffffffLL) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16) return RV_ERR_ALIGNMENT;
+    if (M == 0) return RV_OK;
+    alignas(64) CUtensorMap map_a, map_b;
+    int st = rv_make_bf16_map(&map_a, x, M, K, BM);
+    if (st != RV_OK) return st;
+    st = rv_make_bf16_map(&map_b, w, groups * N, K, BN / 2);
+    if (st != RV_OK) return st;
+    GemmParams p = {};
+    p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
+    p.splits = 1; p.tile_group = tile_group;
+    p.m_tiles = M / TILE_ROWS;
+    p.n_tiles = epilogue == EPI_GATED ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
+    return launch_gemm(map_a, map_b, p, 0, stream);
 }
 
 // The q/k/v product of an attention layer for many rows, with bias, rotation and the cache write in

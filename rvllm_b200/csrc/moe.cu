@@ -11,6 +11,14 @@
 // feature at a time and its lanes walk the weight row (16-byte loads where rows are aligned).  The weights of an
 // expert are read once per token that chose it: the kernels serve decoded tokens and short portions, where the step
 // is bound by reading the chosen experts' weights; sums are float, in one order whatever the batch.
+//
+// Many tokens take another way, on the tensor cores: the (token, slot) pairs are sorted by expert into a buffer in
+// which every expert's rows are padded to whole row tiles, and two grouped products (gemm_tcgen05.cu: row tile t is
+// multiplied with the matrices of expert tile_group[t]) run over it.  The kernels here do the sorting and the sum:
+//
+//   moe_route     row_of[pair], src_of[row], tile_group[tile] from chosen (one CTA: counts, padded offsets, places)
+//   moe_gather    xs[row] = x[src_of[row]], zeros in the padding
+//   moe_combine   out[t] = (add[t]) + weight * sum_k ys[row_of[t * top + k]]   (slots in their order: one sum per element)
 #include "common.cuh"
 
 template <typename T> __device__ __forceinline__ float moe_dot(const T* __restrict__ w, const float* __restrict__ x, int n, int lane);
@@ -146,4 +154,112 @@ RV_EXPORT int rv_moe_experts(const void* x, const int* chosen, const void* gate_
     if (dtype == RV_DTYPE_BF16)
         return moe_launch<__nv_bfloat16>(x, chosen, gate_up, down, act, add, out, out_f32, tokens, top, experts, ff, width, weight, 3, stream);
     return RV_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------ sorting pairs by expert for the grouped products
+// One CTA.  Shared memory: counts[experts], offsets[experts], cursor[experts].
+__global__ void __launch_bounds__(1024)
+moe_route_kernel(const int* __restrict__ chosen, int pairs, int top, int experts, int tile_rows, int max_tiles,
+                 int* __restrict__ row_of, int* __restrict__ src_of, int* __restrict__ tile_group) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    extern __shared__ int sm[];
+    int* counts = sm;
+    int* offsets = sm + experts;
+    int* cursor = sm + 2 * experts;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+    for (int r = threadIdx.x; r < max_tiles * tile_rows; r += blockDim.x) src_of[r] = -1;
+    for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_group[t] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) {
+            offsets[e] = at;
+            at += (counts[e] + tile_rows - 1) / tile_rows * tile_rows;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const int first = offsets[e] / tile_rows, n = (counts[e] + tile_rows - 1) / tile_rows;
+        for (int t = 0; t < n && first + t < max_tiles; ++t) tile_group[first + t] = e;
+    }
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        int row = -1;
+        if (e >= 0 && e < experts) {
+            row = offsets[e] + atomicAdd(&cursor[e], 1);
+            if (row < max_tiles * tile_rows) src_of[row] = i / top; else row = -1;
+        }
+        row_of[i] = row;
+    }
+}
+
+// xs[row, :] = x[src_of[row], :] or zeros; 16-byte words (`words` per row)
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ src_of, uint4* __restrict__ xs, int words,
+                                  size_t total) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / words;
+        const int src = src_of[row];
+        xs[i] = src >= 0 ? x[(size_t)src * words + (i - row * words)] : make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+template <typename TO>
+__global__ void moe_combine_kernel(const float* __restrict__ ys, const int* __restrict__ row_of, const float* add, TO* out,
+                                   int top, int width, float weight, size_t total) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / width;
+        const int n = (int)(i - t * width);
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int row = row_of[t * top + k];
+            if (row >= 0) s += ys[(size_t)row * width + n];
+        }
+        float v = s * weight;
+        if (add) v += add[i];
+        out[i] = rv_from_float<TO>(v);
+    }
+}
+
+RV_EXPORT int rv_moe_route(const int* chosen, int pairs, int top, int experts, int tile_rows, int max_tiles, int* row_of, int* src_of,
+                           int* tile_group, cudaStream_t stream) {
+    if (pairs < 0 || top <= 0 || experts <= 0 || tile_rows <= 0 || max_tiles <= 0) return RV_ERR_BAD_SIZE;
+    if (experts > 4096) return RV_ERR_UNSUPPORTED;
+    if ((long long)max_tiles * tile_rows < (long long)pairs) return RV_ERR_BAD_SIZE;
+    RV_LAUNCH_ST = rv_launch(moe_route_kernel, dim3(1), dim3(1024), (size_t)3 * experts * sizeof(int), stream, chosen, pairs, top, experts,
+                             tile_rows, max_tiles, row_of, src_of, tile_group);
+    return rv_launch_status();
+}
+
+RV_EXPORT int rv_moe_gather(const void* x, const int* src_of, void* xs, int rows, int width_bytes, cudaStream_t stream) {
+    if (rows < 0 || width_bytes <= 0 || width_bytes % 16) return RV_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(xs)) % 16) return RV_ERR_ALIGNMENT;
+    if (rows == 0) return RV_OK;
+    const size_t total = (size_t)rows * (width_bytes / 16);
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    RV_LAUNCH_ST = rv_launch(moe_gather_kernel, dim3(blocks), dim3(256), 0, stream, (const uint4*)x, src_of, (uint4*)xs, width_bytes / 16, total);
+    return rv_launch_status();
+}
+
+RV_EXPORT int rv_moe_combine(const float* ys, const int* row_of, const float* add, void* out, int out_f32, int tokens, int top,
+                             int width, float weight, cudaStream_t stream) {
+    if (tokens < 0 || top <= 0 || width <= 0) return RV_ERR_BAD_SIZE;
+    if (tokens == 0) return RV_OK;
+    const size_t total = (size_t)tokens * width;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (out_f32)
+        RV_LAUNCH_ST = rv_launch(moe_combine_kernel<float>, dim3(blocks), dim3(256), 0, stream, ys, row_of, add, (float*)out, top, width, weight, total);
+    else
+        RV_LAUNCH_ST = rv_launch(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, ys, row_of, add, (__nv_bfloat16*)out, top,
+                                 width, weight, total);
+    return rv_launch_status();
 }

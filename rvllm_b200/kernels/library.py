@@ -1150,6 +1150,8 @@ class CudaKernels:
         out_dtype = out_dtype or x.dtype
         if out_dtype not in (x.dtype, torch.float32):
             raise KernelError(f"moe_experts: result type {out_dtype} for operands of {x.dtype}")
+        if x.dtype == torch.bfloat16 and T >= self.MOE_GROUPED_MIN_TOKENS and width % 8 == 0 and ff % 8 == 0 and E <= 4096:
+            return self._moe_grouped(x, chosen, gate_up, down, weight, add, out_dtype)
         act = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
         out = torch.empty((T, width), dtype=out_dtype, device=x.device)
         st = self._lib("moe.cu").rv_moe_experts(
@@ -1157,6 +1159,43 @@ class CudaKernels:
             c_int(T), c_int(top), c_int(E), c_int(ff), c_int(width), c_float(weight), c_int(self._dt(x, "x")), self._stream())
         _check("moe_experts", st)
         COUNTERS['launches'] += 1
+        return out
+
+    MOE_GROUPED_MIN_TOKENS = 128      # tokens of a step from which the experts' products run grouped on the tcgen05 GEMM
+
+    def _moe_grouped(self, x, chosen, gate_up, down, weight, add, out_dtype):
+        """`moe_experts` for many bfloat16 tokens: the (token, slot) pairs sorted by expert, every expert's rows padded to
+        whole row tiles, two grouped tcgen05 products over the sorted rows (gate/up with the SiLU epilogue, then down with a
+        float32 result), and the weighted sum per token.  Everything is decided on the device; the buffers are sized for
+        the worst case (every expert's last tile nearly empty)."""
+        T, width = x.shape
+        E, ff2, _ = gate_up.shape
+        ff, top = ff2 // 2, chosen.shape[1]
+        lib = self._lib("gemm_tcgen05.cu", ())
+        moe = self._lib("moe.cu")
+        R = int(lib.rv_gemm_tcgen05_row_tile())
+        pairs = T * top
+        max_tiles = (pairs + E * (R - 1)) // R
+        rows = max_tiles * R
+        dev = x.device
+        row_of = torch.empty((pairs,), dtype=torch.int32, device=dev)
+        src_of = torch.empty((rows,), dtype=torch.int32, device=dev)
+        tile_group = torch.empty((max_tiles,), dtype=torch.int32, device=dev)
+        _check("moe_route", moe.rv_moe_route(_ptr(chosen), c_int(pairs), c_int(top), c_int(E), c_int(R), c_int(max_tiles), _ptr(row_of),
+                                             _ptr(src_of), _ptr(tile_group), self._stream()))
+        xs = torch.empty((rows, width), dtype=torch.bfloat16, device=dev)
+        _check("moe_gather", moe.rv_moe_gather(_ptr(x), _ptr(src_of), _ptr(xs), c_int(rows), c_int(width * 2), self._stream()))
+        act = torch.empty((rows, ff), dtype=torch.bfloat16, device=dev)
+        _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
+            _ptr(xs), _ptr(gate_up), _ptr(tile_group), _ptr(act), c_int(0), c_int(rows), c_int(ff2), c_int(width), c_int(E), c_int(2),
+            _ptr(self._status), self._stream()))
+        ys = torch.empty((rows, width), dtype=torch.float32, device=dev)
+        _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
+            _ptr(act), _ptr(down), _ptr(tile_group), _ptr(ys), c_int(1), c_int(rows), c_int(width), c_int(ff), c_int(E), c_int(0),
+            _ptr(self._status), self._stream()))
+        out = torch.empty((T, width), dtype=out_dtype, device=dev)
+        _check("moe_combine", moe.rv_moe_combine(_ptr(ys), _ptr(row_of), _ptr(add), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
+                                                 c_int(T), c_int(top), c_int(width), c_float(weight), self._stream()))
         return out
 
     # ------------------------------------------------------------------ sampling

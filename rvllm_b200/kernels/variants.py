@@ -7,6 +7,8 @@ from . import build
 
 
 FLASH_HEAD_DIMS = (16, 32, 64, 128)
+# one-plane builds (row, leading part read as the value) for latent attention: the benchmark's layer sizes
+FLASH_LATENT_ROWS = ((256, 192),)
 
 
 def all_variants() -> List[Tuple[str, Sequence[str]]]:
@@ -16,6 +18,7 @@ def all_variants() -> List[Tuple[str, Sequence[str]]]:
             # one library per head size; the build check compiles the sizes of the benchmark
             # and test configurations, others are compiled when a model first needs them
             out.extend((src, (f"-DHEAD_DIM={hd}",)) for hd in FLASH_HEAD_DIMS)
+            out.extend((src, (f"-DHEAD_DIM={row}", f"-DV_DIM={vd}", "-DKV_PLANES=1")) for row, vd in FLASH_LATENT_ROWS)
         elif src == "attention_tcgen05.cu":
             out.extend((src, (f"-DHEAD_DIM={hd}",)) for hd in (64, 128))
         elif src == "gemm_tcgen05.cu":
