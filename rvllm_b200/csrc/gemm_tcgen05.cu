@@ -96,11 +96,14 @@ struct GemmParams {
     const float* sin_t;
     int nh, nkv, hd, page_size, table_rows;
     int act;                       // EPI_GATED: 0 SiLU, 1 the tanh form of GELU
-    // Grouped product (plain and gated epilogues, the build on single CTAs): W holds `groups` matrices of N rows one
-    // below the other, and row tile t of x (TILE_ROWS rows) is multiplied with matrix tile_group[t]; a negative entry
-    // marks a row tile that nobody uses, which every role of the kernel skips.  The rows of x are sorted by group
-    // and every group's rows padded to whole tiles by the caller (the experts of a mixture).
+    // Grouped product (plain and gated epilogues): W holds `groups` matrices of N rows one below the other, and work
+    // unit t (m_tiles of them) multiplies rows of x with matrix tile_group[t]; a negative entry marks a unit that nobody
+    // uses, which every role of the kernel skips.  The rows of x are sorted by group and every group's rows padded to
+    // whole blocks of BM rows by the caller (the experts of a mixture).  A unit is one block of BM rows per CTA of the
+    // tile (two on the build for pairs): tile_rows[t * ranks + rank] is the first row of that CTA's block, or negative
+    // where a group has an odd number of blocks - that CTA then loads its partner's rows again and stores nothing.
     const int* tile_group;         // [m_tiles] or nullptr
+    const int* tile_rows;          // [m_tiles * (RV_PAIR ? 2 : 1)]
 };
 
 
@@ -284,10 +287,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int issued = 0;
             bool ok = true;
             for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
-                const int m0 = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM;      // this CTA's 128 rows
+                int m0 = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM;            // this CTA's 128 rows
                 const int nt = tile / p.m_tiles;
                 const int grp = p.tile_group ? __ldg(p.tile_group + tile % p.m_tiles) : 0;
-                if (grp < 0) continue;                                              // a row tile without rows
+                if (grp < 0) continue;                                              // a unit without rows
+                if (p.tile_group) {
+                    const int* rows = p.tile_rows + (tile % p.m_tiles) * (RV_PAIR ? 2 : 1);
+                    m0 = __ldg(rows + rank);
+                    if (m0 < 0) m0 = __ldg(rows);                                   // no block of its own: the partner's again
+                }
                 const int w_base = grp * p.N;                                       // the group's first row of W
                 for (int kb = kb_first; kb < kb_last; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, &abort_flag, 1)) { ok = false; break; }
@@ -387,7 +395,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 break;
             }
             tcgen05_fence_after();
-            const int m = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM + quarter * 32 + lane;
+            int m = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM + quarter * 32 + lane;
+            if (p.tile_group) {
+                const int first = __ldg(p.tile_rows + (tile % p.m_tiles) * (RV_PAIR ? 2 : 1) + rank);
+                m = first < 0 ? p.M : first + quarter * 32 + lane;                  // (rows from M on are never stored)
+            }
             const int nt = tile / p.m_tiles;
             const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quarter * 32) << 16);
             // ---- K in parts over a cluster: every CTA keeps cols_per columns of the tile.  After the cluster's barrier
@@ -662,17 +674,18 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
     return launch_gemm(map_a, map_b, p, max_ctas, stream);
 }
 
-// The grouped product: x [M, K] with M a multiple of the row tile, rows sorted by group and padded per group;
-// w [groups * N, K]; tile_group [M / row tile] on the device (negative: tile unused); out [M, N] (gated: N / 2 columns).
-// epilogue 0 (plain) or 2 (gated, SiLU).  The build on single CTAs only (row tiles of 128).
-RV_EXPORT int rv_gemm_tcgen05_row_tile() { return TILE_ROWS; }
+// The grouped product: x [M, K], rows sorted by group, every group's rows padded to whole blocks of 128;
+// w [groups * N, K]; on the device tile_group [units] (negative: unit unused) and tile_rows [units * ranks] (first row of
+// each CTA's block, negative: none), ranks = rv_gemm_tcgen05_ranks(); out [M, N] (gated: N / 2 columns).
+// epilogue 0 (plain) or 2 (gated, SiLU).
+RV_EXPORT int rv_gemm_tcgen05_block_rows() { return BM; }
+RV_EXPORT int rv_gemm_tcgen05_ranks() { return RV_PAIR ? 2 : 1; }
 
-RV_EXPORT int rv_gemm_tcgen05_grouped(const void* x, const void* w, const int* tile_group, void* out, int out_f32,
-                                      int M, int N, int K, int groups, int epilogue, int* status, cudaStream_t stream) {
-    if (RV_PAIR) return RV_ERR_UNSUPPORTED;
-    if (M < 0 || N <= 0 || K <= 0 || groups <= 0 || !tile_group) return RV_ERR_BAD_SIZE;
+RV_EXPORT int rv_gemm_tcgen05_grouped(const void* x, const void* w, const int* tile_group, const int* tile_rows, void* out, int out_f32,
+                                      int M, int N, int K, int groups, int units, int epilogue, int* status, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || groups <= 0 || units <= 0 || !tile_group || !tile_rows) return RV_ERR_BAD_SIZE;
     if (epilogue != EPI_PLAIN && epilogue != EPI_GATED) return RV_ERR_UNSUPPORTED;
-    if (K % 8 || M % TILE_ROWS) return RV_ERR_UNSUPPORTED;
+    if (K % 8 || M % BM) return RV_ERR_UNSUPPORTED;
     if (epilogue == EPI_GATED && (N & 1)) return RV_ERR_BAD_SIZE;
     if ((long long)groups * N > 0x7fffffffLL) return RV_ERR_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16) return RV_ERR_ALIGNMENT;
@@ -684,8 +697,8 @@ RV_EXPORT int rv_gemm_tcgen05_grouped(const void* x, const void* w, const int* t
     if (st != RV_OK) return st;
     GemmParams p = {};
     p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
-    p.splits = 1; p.tile_group = tile_group;
-    p.m_tiles = M / TILE_ROWS;
+    p.splits = 1; p.tile_group = tile_group; p.tile_rows = tile_rows;
+    p.m_tiles = units;
     p.n_tiles = epilogue == EPI_GATED ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
     return launch_gemm(map_a, map_b, p, 0, stream);
 }

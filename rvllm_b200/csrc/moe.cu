@@ -16,46 +16,57 @@
 // which every expert's rows are padded to whole row tiles, and two grouped products (gemm_tcgen05.cu: row tile t is
 // multiplied with the matrices of expert tile_group[t]) run over it.  The kernels here do the sorting and the sum:
 //
-//   moe_route     row_of[pair], src_of[row], tile_group[tile] from chosen (one CTA: counts, padded offsets, places)
+//   moe_route     row_of[pair], src_of[row] and the products' work units (tile_group, tile_rows) from chosen (one CTA:
+//                 counts, padded offsets, places)
 //   moe_gather    xs[row] = x[src_of[row]], zeros in the padding
 //   moe_combine   out[t] = (add[t]) + weight * sum_k ys[row_of[t * top + k]]   (slots in their order: one sum per element)
 #include "common.cuh"
 
-template <typename T> __device__ __forceinline__ float moe_dot(const T* __restrict__ w, const float* __restrict__ x, int n, int lane);
-
-template <> __device__ __forceinline__ float moe_dot<float>(const float* __restrict__ w, const float* __restrict__ x, int n, int lane) {
-    float s = 0.f;
-    if ((n & 3) == 0 && ((uintptr_t)w & 15) == 0) {
-        for (int i = lane * 4; i < n; i += 128) {
-            const float4 v = *reinterpret_cast<const float4*>(w + i);
-            s = fmaf(v.x, x[i], s); s = fmaf(v.y, x[i + 1], s); s = fmaf(v.z, x[i + 2], s); s = fmaf(v.w, x[i + 3], s);
-        }
-    } else {
-        for (int i = lane; i < n; i += 32) s = fmaf(w[i], x[i], s);
-    }
-    return rv_warp_sum(s);
-}
-
-template <> __device__ __forceinline__ float moe_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ x, int n, int lane) {
-    float s = 0.f;
-    if ((n & 7) == 0 && ((uintptr_t)w & 15) == 0) {
-        for (int i = lane * 8; i < n; i += 256) {
-            const uint4 v = *reinterpret_cast<const uint4*>(w + i);
-            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+// N rows of W against one vector at a time: the lanes walk all rows together, so N loads are in flight per lane and step
+// (one row after the other left the memory idle between a row's reduction and the next row's first load).
+template <typename T, int N>
+__device__ __forceinline__ void moe_dot_rows(const T* const (&w)[N], const float* __restrict__ x, int n, int lane, float (&out)[N]) {
+    float s[N];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __bfloat1622float2(p[j]);
-                s = fmaf(f.x, x[i + 2 * j], s); s = fmaf(f.y, x[i + 2 * j + 1], s);
+    for (int r = 0; r < N; ++r) s[r] = 0.f;
+    constexpr int V = 16 / sizeof(T);                      // elements of a 16-byte load
+    bool aligned = (n % V) == 0;
+#pragma unroll
+    for (int r = 0; r < N; ++r) aligned = aligned && ((uintptr_t)w[r] & 15) == 0;
+    if (aligned) {
+        for (int i = lane * V; i < n; i += 32 * V) {
+            uint4 v[N];
+#pragma unroll
+            for (int r = 0; r < N; ++r) v[r] = __ldg(reinterpret_cast<const uint4*>(w[r] + i));
+#pragma unroll
+            for (int r = 0; r < N; ++r) {
+                if constexpr (sizeof(T) == 4) {
+                    const float* f = reinterpret_cast<const float*>(&v[r]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) s[r] = fmaf(f[j], x[i + j], s[r]);
+                } else {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[r]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __bfloat1622float2(h[j]);
+                        s[r] = fmaf(f.x, x[i + 2 * j], s[r]);
+                        s[r] = fmaf(f.y, x[i + 2 * j + 1], s[r]);
+                    }
+                }
             }
         }
     } else {
-        for (int i = lane; i < n; i += 32) s = fmaf(__bfloat162float(w[i]), x[i], s);
+        for (int i = lane; i < n; i += 32)
+#pragma unroll
+            for (int r = 0; r < N; ++r) s[r] = fmaf(rv_to_float(w[r][i]), x[i], s[r]);
     }
-    return rv_warp_sum(s);
+#pragma unroll
+    for (int r = 0; r < N; ++r) out[r] = rv_warp_sum(s[r]);
 }
 
 #define MOE_WARPS 8
 #define MOE_FEATURES 32      // features of one CTA
+#define MOE_PER_WARP (MOE_FEATURES / MOE_WARPS)
 
 // grid (tokens * top, feature blocks)
 template <typename T>
@@ -77,10 +88,21 @@ moe_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ chosen, cons
     __syncthreads();
     const T* wg = gate_up + (size_t)e * 2 * ff * width;
     const T* wu = wg + (size_t)ff * width;
-    for (int f = f0 + warp; f < min(ff, f0 + MOE_FEATURES); f += MOE_WARPS) {
-        const float g = moe_dot<T>(wg + (size_t)f * width, xs, width, lane);
-        const float u = moe_dot<T>(wu + (size_t)f * width, xs, width, lane);
-        if (lane == 0) act[(size_t)pair * ff + f] = rv_from_float<T>(g / (1.0f + expf(-g)) * u);
+    // a warp's features f0 + warp, + MOE_WARPS, ...: their gate and up rows are walked together (a feature beyond ff reads
+    // the last row again and is not stored)
+    const T* rows[2 * MOE_PER_WARP];
+#pragma unroll
+    for (int j = 0; j < MOE_PER_WARP; ++j) {
+        const int f = min(ff - 1, f0 + warp + j * MOE_WARPS);
+        rows[2 * j] = wg + (size_t)f * width;
+        rows[2 * j + 1] = wu + (size_t)f * width;
+    }
+    float r[2 * MOE_PER_WARP];
+    moe_dot_rows<T, 2 * MOE_PER_WARP>(rows, xs, width, lane, r);
+#pragma unroll
+    for (int j = 0; j < MOE_PER_WARP; ++j) {
+        const int f = f0 + warp + j * MOE_WARPS;
+        if (lane == 0 && f < ff) act[(size_t)pair * ff + f] = rv_from_float<T>(r[2 * j] / (1.0f + expf(-r[2 * j])) * r[2 * j + 1]);
     }
 }
 
@@ -97,15 +119,25 @@ moe_down_kernel(const T* __restrict__ act, const int* __restrict__ chosen, const
     for (int i = threadIdx.x; i < top * ff; i += blockDim.x) as[i] = rv_to_float(act[(size_t)t * top * ff + i]);
     __syncthreads();
     const int n0 = blockIdx.y * MOE_FEATURES;
-    for (int n = n0 + warp; n < min(width, n0 + MOE_FEATURES); n += MOE_WARPS) {
-        float s = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int e = chosen[t * top + k];
-            if (e < 0 || e >= experts) continue;
-            s += moe_dot<T>(down + ((size_t)e * width + n) * ff, as + (size_t)k * ff, ff, lane);
-        }
-        if (lane == 0) {
-            float v = s * weight;
+    float sum[MOE_PER_WARP];
+#pragma unroll
+    for (int j = 0; j < MOE_PER_WARP; ++j) sum[j] = 0.f;
+    for (int k = 0; k < top; ++k) {                       // the slots in their order: one sum per element, whatever the batch
+        const int e = chosen[t * top + k];
+        if (e < 0 || e >= experts) continue;
+        const T* rows[MOE_PER_WARP];
+#pragma unroll
+        for (int j = 0; j < MOE_PER_WARP; ++j) rows[j] = down + ((size_t)e * width + min(width - 1, n0 + warp + j * MOE_WARPS)) * ff;
+        float r[MOE_PER_WARP];
+        moe_dot_rows<T, MOE_PER_WARP>(rows, as + (size_t)k * ff, ff, lane, r);
+#pragma unroll
+        for (int j = 0; j < MOE_PER_WARP; ++j) sum[j] += r[j];
+    }
+#pragma unroll
+    for (int j = 0; j < MOE_PER_WARP; ++j) {
+        const int n = n0 + warp + j * MOE_WARPS;
+        if (lane == 0 && n < width) {
+            float v = sum[j] * weight;
             if (add) v += add[(size_t)t * width + n];
             out[(size_t)t * width + n] = rv_from_float<TO>(v);
         }
@@ -157,19 +189,23 @@ RV_EXPORT int rv_moe_experts(const void* x, const int* chosen, const void* gate_
 }
 
 // ------------------------------------------------------------------ sorting pairs by expert for the grouped products
-// One CTA.  Shared memory: counts[experts], offsets[experts], cursor[experts].
+// One CTA.  Shared memory: counts[experts], offsets[experts], cursor[experts], first unit[experts].
+// Rows: expert e gets ceil(count / block) blocks of `block` rows from offsets[e] on.  Work units of the grouped product:
+// `ranks` blocks of one expert each (the CTAs of a tile); where an expert's blocks run out, the unit's last entries are -1.
 __global__ void __launch_bounds__(1024)
-moe_route_kernel(const int* __restrict__ chosen, int pairs, int top, int experts, int tile_rows, int max_tiles,
-                 int* __restrict__ row_of, int* __restrict__ src_of, int* __restrict__ tile_group) {
+moe_route_kernel(const int* __restrict__ chosen, int pairs, int top, int experts, int block, int max_rows, int ranks, int max_units,
+                 int* __restrict__ row_of, int* __restrict__ src_of, int* __restrict__ tile_group, int* __restrict__ tile_rows) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     extern __shared__ int sm[];
     int* counts = sm;
     int* offsets = sm + experts;
     int* cursor = sm + 2 * experts;
+    int* unit0 = sm + 3 * experts;
     for (int e = threadIdx.x; e < experts; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
-    for (int r = threadIdx.x; r < max_tiles * tile_rows; r += blockDim.x) src_of[r] = -1;
-    for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_group[t] = -1;
+    for (int r = threadIdx.x; r < max_rows; r += blockDim.x) src_of[r] = -1;
+    for (int t = threadIdx.x; t < max_units; t += blockDim.x) tile_group[t] = -1;
+    for (int t = threadIdx.x; t < max_units * ranks; t += blockDim.x) tile_rows[t] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
         const int e = chosen[i];
@@ -177,23 +213,31 @@ moe_route_kernel(const int* __restrict__ chosen, int pairs, int top, int experts
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        int at = 0;
+        int at = 0, unit = 0;
         for (int e = 0; e < experts; ++e) {
+            const int blocks = (counts[e] + block - 1) / block;
             offsets[e] = at;
-            at += (counts[e] + tile_rows - 1) / tile_rows * tile_rows;
+            unit0[e] = unit;
+            at += blocks * block;
+            unit += (blocks + ranks - 1) / ranks;
         }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-        const int first = offsets[e] / tile_rows, n = (counts[e] + tile_rows - 1) / tile_rows;
-        for (int t = 0; t < n && first + t < max_tiles; ++t) tile_group[first + t] = e;
+        const int blocks = (counts[e] + block - 1) / block;
+        for (int b = 0; b < blocks; ++b) {
+            const int unit = unit0[e] + b / ranks;
+            if (unit >= max_units) break;
+            tile_group[unit] = e;
+            tile_rows[unit * ranks + b % ranks] = offsets[e] + b * block;
+        }
     }
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
         const int e = chosen[i];
         int row = -1;
         if (e >= 0 && e < experts) {
             row = offsets[e] + atomicAdd(&cursor[e], 1);
-            if (row < max_tiles * tile_rows) src_of[row] = i / top; else row = -1;
+            if (row < max_rows) src_of[row] = i / top; else row = -1;
         }
         row_of[i] = row;
     }
@@ -230,13 +274,13 @@ __global__ void moe_combine_kernel(const float* __restrict__ ys, const int* __re
     }
 }
 
-RV_EXPORT int rv_moe_route(const int* chosen, int pairs, int top, int experts, int tile_rows, int max_tiles, int* row_of, int* src_of,
-                           int* tile_group, cudaStream_t stream) {
-    if (pairs < 0 || top <= 0 || experts <= 0 || tile_rows <= 0 || max_tiles <= 0) return RV_ERR_BAD_SIZE;
+RV_EXPORT int rv_moe_route(const int* chosen, int pairs, int top, int experts, int block, int max_rows, int ranks, int max_units,
+                           int* row_of, int* src_of, int* tile_group, int* tile_rows, cudaStream_t stream) {
+    if (pairs < 0 || top <= 0 || experts <= 0 || block <= 0 || max_rows <= 0 || ranks <= 0 || max_units <= 0) return RV_ERR_BAD_SIZE;
     if (experts > 4096) return RV_ERR_UNSUPPORTED;
-    if ((long long)max_tiles * tile_rows < (long long)pairs) return RV_ERR_BAD_SIZE;
-    RV_LAUNCH_ST = rv_launch(moe_route_kernel, dim3(1), dim3(1024), (size_t)3 * experts * sizeof(int), stream, chosen, pairs, top, experts,
-                             tile_rows, max_tiles, row_of, src_of, tile_group);
+    if ((long long)max_rows < (long long)pairs) return RV_ERR_BAD_SIZE;
+    RV_LAUNCH_ST = rv_launch(moe_route_kernel, dim3(1), dim3(1024), (size_t)4 * experts * sizeof(int), stream, chosen, pairs, top, experts,
+                             block, max_rows, ranks, max_units, row_of, src_of, tile_group, tile_rows);
     return rv_launch_status();
 }
 

@@ -110,25 +110,63 @@ RV_EXPORT int rv_stream_add(float* x, const float* e, const void* v, int v_dtype
 }
 
 // out = a n(z) + b n(z^2) + c n(z^3) + e, n(v) = v / sqrt(mean(v^2) + eps) over the row; coef = (a, b, c, e) float.
-__global__ void __launch_bounds__(256)
+// The row is read once: it waits in shared memory (as float) between the pass that gathers the three mean squares and
+// the pass that writes; rows too long for that are read twice.
+__global__ void __launch_bounds__(512)
 polynorm_kernel(const void* __restrict__ z, int z_dtype, const float* __restrict__ coef, void* __restrict__ out, int out_dtype,
-                int cols, float eps) {
+                int cols, float eps, int keep) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
+    extern __shared__ float row[];
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * cols;
     float s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-        const float v = rv_load_any(z, z_dtype, base + i), v2 = v * v, v3 = v2 * v;
-        s1 = fmaf(v, v, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+    const bool vec = keep && z_dtype == RV_DTYPE_F32 && (cols & 3) == 0 && (reinterpret_cast<uintptr_t>(z) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(out) & 15) == 0;      // float rows in 16-byte words
+    if (vec) {
+        const float4* src = reinterpret_cast<const float4*>((const float*)z + base);
+        for (int i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            const float4 q = src[i];
+            reinterpret_cast<float4*>(row)[i] = q;
+            const float v[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float v2 = v[j] * v[j], v3 = v2 * v[j];
+                s1 = fmaf(v[j], v[j], s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+            const float v = rv_load_any(z, z_dtype, base + i), v2 = v * v, v3 = v2 * v;
+            if (keep) row[i] = v;
+            s1 = fmaf(v, v, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+        }
     }
     s1 = rv_block_sum(s1, scratch);
     s2 = rv_block_sum(s2, scratch);
     s3 = rv_block_sum(s3, scratch);
     const float n = (float)cols;
     const float a = coef[0] / sqrtf(s1 / n + eps), b = coef[1] / sqrtf(s2 / n + eps), c = coef[2] / sqrtf(s3 / n + eps), e = coef[3];
+    if (vec) {
+        for (int i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            const float4 q = reinterpret_cast<const float4*>(row)[i];
+            const float v[4] = {q.x, q.y, q.z, q.w};
+            float r[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float v2 = v[j] * v[j]; r[j] = a * v[j] + b * v2 + c * (v2 * v[j]) + e; }
+            if (out_dtype == RV_DTYPE_F32) {
+                reinterpret_cast<float4*>((float*)out + base)[i] = make_float4(r[0], r[1], r[2], r[3]);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+                uint2 w;
+                w.x = *reinterpret_cast<uint32_t*>(&lo); w.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>((__nv_bfloat16*)out + base)[i] = w;
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-        const float v = rv_load_any(z, z_dtype, base + i), v2 = v * v;
+        const float v = keep ? row[i] : rv_load_any(z, z_dtype, base + i), v2 = v * v;
         rv_store_any(out, out_dtype, base + i, a * v + b * v2 + c * (v2 * v) + e);
     }
 }
@@ -138,8 +176,11 @@ RV_EXPORT int rv_polynorm(const void* z, int z_dtype, const float* coef, void* o
     if (rows < 0 || cols <= 0) return RV_ERR_BAD_SIZE;
     if ((z_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
     if (rows == 0) return RV_OK;
-    RV_LAUNCH_ST = rv_launch(polynorm_kernel, dim3(rows), dim3(cols >= 1024 ? 256 : 128), 0, stream, z, z_dtype, coef, out, out_dtype,
-                             cols, eps);
+    const int keep = cols <= 24 * 1024 ? 1 : 0;            // 96 KB of floats: two CTAs still fit an SM
+    static RvPerDevice configured;
+    if (int st = rv_configure_smem(configured, polynorm_kernel, 96 * 1024)) return st;
+    RV_LAUNCH_ST = rv_launch(polynorm_kernel, dim3(rows), dim3(cols >= 4096 ? 512 : (cols >= 1024 ? 256 : 128)), keep ? (size_t)cols * 4 : 0,
+                             stream, z, z_dtype, coef, out, out_dtype, cols, eps, keep);
     return rv_launch_status();
 }
 

@@ -1161,38 +1161,41 @@ class CudaKernels:
         COUNTERS['launches'] += 1
         return out
 
-    MOE_GROUPED_MIN_TOKENS = 128      # tokens of a step from which the experts' products run grouped on the tcgen05 GEMM
+    MOE_GROUPED_MIN_TOKENS = 128      # tokens of a step from which the experts' products run grouped on the tcgen05 GEMM ...
+    MOE_GROUPED_PAIRS = True          # ... on pairs of CTAs (cta_group::2): two blocks of 128 rows of one expert share every tile of its weights
 
     def _moe_grouped(self, x, chosen, gate_up, down, weight, add, out_dtype):
         """`moe_experts` for many bfloat16 tokens: the (token, slot) pairs sorted by expert, every expert's rows padded to
-        whole row tiles, two grouped tcgen05 products over the sorted rows (gate/up with the SiLU epilogue, then down with a
+        whole blocks of 128, two grouped tcgen05 products over the sorted rows (gate/up with the SiLU epilogue, then down with a
         float32 result), and the weighted sum per token.  Everything is decided on the device; the buffers are sized for
-        the worst case (every expert's last tile nearly empty)."""
+        the worst case (every expert's last block nearly empty)."""
         T, width = x.shape
         E, ff2, _ = gate_up.shape
         ff, top = ff2 // 2, chosen.shape[1]
-        lib = self._lib("gemm_tcgen05.cu", ())
+        lib = self._lib("gemm_tcgen05.cu", ("-DRV_PAIR=1",) if self.MOE_GROUPED_PAIRS else ())
         moe = self._lib("moe.cu")
-        R = int(lib.rv_gemm_tcgen05_row_tile())
+        R, ranks = int(lib.rv_gemm_tcgen05_block_rows()), int(lib.rv_gemm_tcgen05_ranks())
         pairs = T * top
-        max_tiles = (pairs + E * (R - 1)) // R
-        rows = max_tiles * R
+        max_blocks = (pairs + E * (R - 1)) // R         # every expert's last block of rows nearly empty
+        units = max_blocks                               # (a unit holds at least one block)
+        rows = max_blocks * R
         dev = x.device
         row_of = torch.empty((pairs,), dtype=torch.int32, device=dev)
         src_of = torch.empty((rows,), dtype=torch.int32, device=dev)
-        tile_group = torch.empty((max_tiles,), dtype=torch.int32, device=dev)
-        _check("moe_route", moe.rv_moe_route(_ptr(chosen), c_int(pairs), c_int(top), c_int(E), c_int(R), c_int(max_tiles), _ptr(row_of),
-                                             _ptr(src_of), _ptr(tile_group), self._stream()))
+        tile_group = torch.empty((units,), dtype=torch.int32, device=dev)
+        tile_rows = torch.empty((units * ranks,), dtype=torch.int32, device=dev)
+        _check("moe_route", moe.rv_moe_route(_ptr(chosen), c_int(pairs), c_int(top), c_int(E), c_int(R), c_int(rows), c_int(ranks),
+                                             c_int(units), _ptr(row_of), _ptr(src_of), _ptr(tile_group), _ptr(tile_rows), self._stream()))
         xs = torch.empty((rows, width), dtype=torch.bfloat16, device=dev)
         _check("moe_gather", moe.rv_moe_gather(_ptr(x), _ptr(src_of), _ptr(xs), c_int(rows), c_int(width * 2), self._stream()))
         act = torch.empty((rows, ff), dtype=torch.bfloat16, device=dev)
         _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
-            _ptr(xs), _ptr(gate_up), _ptr(tile_group), _ptr(act), c_int(0), c_int(rows), c_int(ff2), c_int(width), c_int(E), c_int(2),
-            _ptr(self._status), self._stream()))
+            _ptr(xs), _ptr(gate_up), _ptr(tile_group), _ptr(tile_rows), _ptr(act), c_int(0), c_int(rows), c_int(ff2), c_int(width), c_int(E),
+            c_int(units), c_int(2), _ptr(self._status), self._stream()))
         ys = torch.empty((rows, width), dtype=torch.float32, device=dev)
         _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
-            _ptr(act), _ptr(down), _ptr(tile_group), _ptr(ys), c_int(1), c_int(rows), c_int(width), c_int(ff), c_int(E), c_int(0),
-            _ptr(self._status), self._stream()))
+            _ptr(act), _ptr(down), _ptr(tile_group), _ptr(tile_rows), _ptr(ys), c_int(1), c_int(rows), c_int(width), c_int(ff), c_int(E),
+            c_int(units), c_int(0), _ptr(self._status), self._stream()))
         out = torch.empty((T, width), dtype=out_dtype, device=dev)
         _check("moe_combine", moe.rv_moe_combine(_ptr(ys), _ptr(row_of), _ptr(add), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
                                                  c_int(T), c_int(top), c_int(width), c_float(weight), self._stream()))
