@@ -102,9 +102,27 @@ struct GemmParams {
     // whole blocks of BM rows by the caller (the experts of a mixture).  A unit is one block of BM rows per CTA of the
     // tile (two on the build for pairs): tile_rows[t * ranks + rank] is the first row of that CTA's block, or negative
     // where a group has an odd number of blocks - that CTA then loads its partner's rows again and stores nothing.
+    // tile_order [m_tiles * n_tiles]: the work of the persistent CTAs in the order they take it, unit * 65536 + column
+    // tile, negative: nothing.  The caller orders it group by group, then column tile by column tile, then the group's
+    // units: CTAs that run side by side then share a group's rows of x and every tile of its matrix through L2, and
+    // both are read from memory once (in the order unit-fastest over ALL units the matrices, which no cache holds,
+    // pushed the rows of x out between two column tiles: 1.8 x the bytes from memory, which bound the time).
     const int* tile_group;         // [m_tiles] or nullptr
     const int* tile_rows;          // [m_tiles * (RV_PAIR ? 2 : 1)]
+    const int* tile_order;         // [m_tiles * n_tiles]
 };
+
+// (unit, column tile) of entry `tile` of the work; false: nothing to do there
+__device__ __forceinline__ bool gemm_tile(const GemmParams& p, int tile, int& unit, int& nt) {
+    if (p.tile_group) {
+        const int w = __ldg(p.tile_order + tile);
+        if (w < 0) return false;
+        unit = w >> 16; nt = w & 0xffff;
+        return true;
+    }
+    unit = tile % p.m_tiles; nt = tile / p.m_tiles;
+    return true;
+}
 
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
@@ -287,12 +305,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int issued = 0;
             bool ok = true;
             for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
-                int m0 = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM;            // this CTA's 128 rows
-                const int nt = tile / p.m_tiles;
-                const int grp = p.tile_group ? __ldg(p.tile_group + tile % p.m_tiles) : 0;
-                if (grp < 0) continue;                                              // a unit without rows
+                int unit, nt;
+                if (!gemm_tile(p, tile, unit, nt)) continue;                        // an entry without work
+                int m0 = unit * TILE_ROWS + (int)rank * BM;                         // this CTA's 128 rows
+                const int grp = p.tile_group ? __ldg(p.tile_group + unit) : 0;
                 if (p.tile_group) {
-                    const int* rows = p.tile_rows + (tile % p.m_tiles) * (RV_PAIR ? 2 : 1);
+                    const int* rows = p.tile_rows + unit * (RV_PAIR ? 2 : 1);
                     m0 = __ldg(rows + rank);
                     if (m0 < 0) m0 = __ldg(rows);                                   // no block of its own: the partner's again
                 }
@@ -351,7 +369,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int local = 0;
             bool ok = true;
             for (int tile = worker; tile < num_tiles && ok; tile += num_workers, ++local) {
-                if (p.tile_group && __ldg(p.tile_group + tile % p.m_tiles) < 0) { --local; continue; }   // (skipped by every role)
+                if (p.tile_group && __ldg(p.tile_order + tile) < 0) { --local; continue; }               // (skipped by every role)
                 const int buf = local & 1;
                 const uint32_t use = (uint32_t)(local >> 1);
                 if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_flag, 2)) { ok = false; break; }
@@ -380,7 +398,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int local = 0;
         bool ok = true;
         for (int tile = worker; tile < num_tiles && ok; tile += num_workers, ++local) {
-            if (p.tile_group && __ldg(p.tile_group + tile % p.m_tiles) < 0) { --local; continue; }
+            if (p.tile_group && __ldg(p.tile_order + tile) < 0) { --local; continue; }
             const int buf = local & 1;
             const uint32_t use = (uint32_t)(local >> 1);
             if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_flag, 4)) {
@@ -395,12 +413,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 break;
             }
             tcgen05_fence_after();
-            int m = (tile % p.m_tiles) * TILE_ROWS + (int)rank * BM + quarter * 32 + lane;
+            int unit, nt;
+            gemm_tile(p, tile, unit, nt);
+            int m = unit * TILE_ROWS + (int)rank * BM + quarter * 32 + lane;
             if (p.tile_group) {
-                const int first = __ldg(p.tile_rows + (tile % p.m_tiles) * (RV_PAIR ? 2 : 1) + rank);
+                const int first = __ldg(p.tile_rows + unit * (RV_PAIR ? 2 : 1) + rank);
                 m = first < 0 ? p.M : first + quarter * 32 + lane;                  // (rows from M on are never stored)
             }
-            const int nt = tile / p.m_tiles;
             const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quarter * 32) << 16);
             // ---- K in parts over a cluster: every CTA keeps cols_per columns of the tile.  After the cluster's barrier
             // (every CTA's products are done, so its stages are free) each thread writes its row's partial of the OTHER
@@ -675,15 +694,19 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
 }
 
 // The grouped product: x [M, K], rows sorted by group, every group's rows padded to whole blocks of 128;
-// w [groups * N, K]; on the device tile_group [units] (negative: unit unused) and tile_rows [units * ranks] (first row of
-// each CTA's block, negative: none), ranks = rv_gemm_tcgen05_ranks(); out [M, N] (gated: N / 2 columns).
-// epilogue 0 (plain) or 2 (gated, SiLU).
+// w [groups * N, K]; on the device tile_group [units] (negative: unit unused), tile_rows [units * ranks] (first row of
+// each CTA's block, negative: none), ranks = rv_gemm_tcgen05_ranks(), and tile_order [units * rv_gemm_tcgen05_column_tiles(N,
+// epilogue)] (see GemmParams); out [M, N] (gated: N / 2 columns).  epilogue 0 (plain) or 2 (gated, SiLU).
+RV_EXPORT int rv_gemm_tcgen05_column_tiles(int N, int epilogue) {
+    return epilogue == EPI_GATED ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
+}
 RV_EXPORT int rv_gemm_tcgen05_block_rows() { return BM; }
 RV_EXPORT int rv_gemm_tcgen05_ranks() { return RV_PAIR ? 2 : 1; }
 
-RV_EXPORT int rv_gemm_tcgen05_grouped(const void* x, const void* w, const int* tile_group, const int* tile_rows, void* out, int out_f32,
-                                      int M, int N, int K, int groups, int units, int epilogue, int* status, cudaStream_t stream) {
-    if (M < 0 || N <= 0 || K <= 0 || groups <= 0 || units <= 0 || !tile_group || !tile_rows) return RV_ERR_BAD_SIZE;
+RV_EXPORT int rv_gemm_tcgen05_grouped(const void* x, const void* w, const int* tile_group, const int* tile_rows, const int* tile_order,
+                                      void* out, int out_f32, int M, int N, int K, int groups, int units, int epilogue, int* status,
+                                      cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || groups <= 0 || units <= 0 || units > 32767 || !tile_group || !tile_rows || !tile_order) return RV_ERR_BAD_SIZE;
     if (epilogue != EPI_PLAIN && epilogue != EPI_GATED) return RV_ERR_UNSUPPORTED;
     if (K % 8 || M % BM) return RV_ERR_UNSUPPORTED;
     if (epilogue == EPI_GATED && (N & 1)) return RV_ERR_BAD_SIZE;
@@ -697,9 +720,10 @@ RV_EXPORT int rv_gemm_tcgen05_grouped(const void* x, const void* w, const int* t
     if (st != RV_OK) return st;
     GemmParams p = {};
     p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
-    p.splits = 1; p.tile_group = tile_group; p.tile_rows = tile_rows;
+    p.splits = 1; p.tile_group = tile_group; p.tile_rows = tile_rows; p.tile_order = tile_order;
     p.m_tiles = units;
-    p.n_tiles = epilogue == EPI_GATED ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
+    p.n_tiles = rv_gemm_tcgen05_column_tiles(N, epilogue);
+    if (p.n_tiles > 65535) return RV_ERR_BAD_SIZE;
     return launch_gemm(map_a, map_b, p, 0, stream);
 }
 

@@ -192,9 +192,11 @@ RV_EXPORT int rv_moe_experts(const void* x, const int* chosen, const void* gate_
 // One CTA.  Shared memory: counts[experts], offsets[experts], cursor[experts], first unit[experts].
 // Rows: expert e gets ceil(count / block) blocks of `block` rows from offsets[e] on.  Work units of the grouped product:
 // `ranks` blocks of one expert each (the CTAs of a tile); where an expert's blocks run out, the unit's last entries are -1.
+// order_a / order_b: the work lists of the two products (nt_a / nt_b column tiles per unit), see GemmParams::tile_order.
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const int* __restrict__ chosen, int pairs, int top, int experts, int block, int max_rows, int ranks, int max_units,
-                 int* __restrict__ row_of, int* __restrict__ src_of, int* __restrict__ tile_group, int* __restrict__ tile_rows) {
+                 int* __restrict__ row_of, int* __restrict__ src_of, int* __restrict__ tile_group, int* __restrict__ tile_rows,
+                 int nt_a, int* __restrict__ order_a, int nt_b, int* __restrict__ order_b) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     extern __shared__ int sm[];
@@ -206,6 +208,8 @@ moe_route_kernel(const int* __restrict__ chosen, int pairs, int top, int experts
     for (int r = threadIdx.x; r < max_rows; r += blockDim.x) src_of[r] = -1;
     for (int t = threadIdx.x; t < max_units; t += blockDim.x) tile_group[t] = -1;
     for (int t = threadIdx.x; t < max_units * ranks; t += blockDim.x) tile_rows[t] = -1;
+    for (int t = threadIdx.x; t < max_units * nt_a; t += blockDim.x) order_a[t] = -1;
+    for (int t = threadIdx.x; t < max_units * nt_b; t += blockDim.x) order_b[t] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
         const int e = chosen[i];
@@ -231,6 +235,10 @@ moe_route_kernel(const int* __restrict__ chosen, int pairs, int top, int experts
             tile_group[unit] = e;
             tile_rows[unit * ranks + b % ranks] = offsets[e] + b * block;
         }
+        // the order of the two products' work: this expert's entries lie together, column tile by column tile, its units within
+        const int units = min((blocks + ranks - 1) / ranks, max(0, max_units - unit0[e]));
+        for (int i = 0; i < units * nt_a; ++i) order_a[unit0[e] * nt_a + i] = ((unit0[e] + i % units) << 16) | (i / units);
+        for (int i = 0; i < units * nt_b; ++i) order_b[unit0[e] * nt_b + i] = ((unit0[e] + i % units) << 16) | (i / units);
     }
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
         const int e = chosen[i];
@@ -275,12 +283,14 @@ __global__ void moe_combine_kernel(const float* __restrict__ ys, const int* __re
 }
 
 RV_EXPORT int rv_moe_route(const int* chosen, int pairs, int top, int experts, int block, int max_rows, int ranks, int max_units,
-                           int* row_of, int* src_of, int* tile_group, int* tile_rows, cudaStream_t stream) {
+                           int* row_of, int* src_of, int* tile_group, int* tile_rows, int nt_a, int* order_a, int nt_b, int* order_b,
+                           cudaStream_t stream) {
     if (pairs < 0 || top <= 0 || experts <= 0 || block <= 0 || max_rows <= 0 || ranks <= 0 || max_units <= 0) return RV_ERR_BAD_SIZE;
+    if (nt_a <= 0 || nt_b <= 0 || nt_a > 65535 || nt_b > 65535 || max_units > 32767 || !order_a || !order_b) return RV_ERR_BAD_SIZE;
     if (experts > 4096) return RV_ERR_UNSUPPORTED;
     if ((long long)max_rows < (long long)pairs) return RV_ERR_BAD_SIZE;
     RV_LAUNCH_ST = rv_launch(moe_route_kernel, dim3(1), dim3(1024), (size_t)4 * experts * sizeof(int), stream, chosen, pairs, top, experts,
-                             block, max_rows, ranks, max_units, row_of, src_of, tile_group, tile_rows);
+                             block, max_rows, ranks, max_units, row_of, src_of, tile_group, tile_rows, nt_a, order_a, nt_b, order_b);
     return rv_launch_status();
 }
 

@@ -1184,17 +1184,21 @@ class CudaKernels:
         src_of = torch.empty((rows,), dtype=torch.int32, device=dev)
         tile_group = torch.empty((units,), dtype=torch.int32, device=dev)
         tile_rows = torch.empty((units * ranks,), dtype=torch.int32, device=dev)
+        nt_a, nt_b = int(lib.rv_gemm_tcgen05_column_tiles(c_int(ff2), c_int(2))), int(lib.rv_gemm_tcgen05_column_tiles(c_int(width), c_int(0)))
+        order_a = torch.empty((units * nt_a,), dtype=torch.int32, device=dev)
+        order_b = torch.empty((units * nt_b,), dtype=torch.int32, device=dev)
         _check("moe_route", moe.rv_moe_route(_ptr(chosen), c_int(pairs), c_int(top), c_int(E), c_int(R), c_int(rows), c_int(ranks),
-                                             c_int(units), _ptr(row_of), _ptr(src_of), _ptr(tile_group), _ptr(tile_rows), self._stream()))
+                                             c_int(units), _ptr(row_of), _ptr(src_of), _ptr(tile_group), _ptr(tile_rows), c_int(nt_a),
+                                             _ptr(order_a), c_int(nt_b), _ptr(order_b), self._stream()))
         xs = torch.empty((rows, width), dtype=torch.bfloat16, device=dev)
         _check("moe_gather", moe.rv_moe_gather(_ptr(x), _ptr(src_of), _ptr(xs), c_int(rows), c_int(width * 2), self._stream()))
         act = torch.empty((rows, ff), dtype=torch.bfloat16, device=dev)
         _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
-            _ptr(xs), _ptr(gate_up), _ptr(tile_group), _ptr(tile_rows), _ptr(act), c_int(0), c_int(rows), c_int(ff2), c_int(width), c_int(E),
+            _ptr(xs), _ptr(gate_up), _ptr(tile_group), _ptr(tile_rows), _ptr(order_a), _ptr(act), c_int(0), c_int(rows), c_int(ff2), c_int(width), c_int(E),
             c_int(units), c_int(2), _ptr(self._status), self._stream()))
         ys = torch.empty((rows, width), dtype=torch.float32, device=dev)
         _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
-            _ptr(act), _ptr(down), _ptr(tile_group), _ptr(tile_rows), _ptr(ys), c_int(1), c_int(rows), c_int(width), c_int(ff), c_int(E),
+            _ptr(act), _ptr(down), _ptr(tile_group), _ptr(tile_rows), _ptr(order_b), _ptr(ys), c_int(1), c_int(rows), c_int(width), c_int(ff), c_int(E),
             c_int(units), c_int(0), _ptr(self._status), self._stream()))
         out = torch.empty((T, width), dtype=out_dtype, device=dev)
         _check("moe_combine", moe.rv_moe_combine(_ptr(ys), _ptr(row_of), _ptr(add), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
