@@ -722,6 +722,9 @@ def run_vipelix(args):
     by_flops("head_linear_absorb", _time_kernel(lambda: K.head_linear(q_plain, uk_t, q_row[:, :, :R]), flush=flush), 2.0 * T * H * R * D, like)
     o_lat = torch.randn(T, H, R, device=dev).to(bf)
     by_flops("head_linear_values", _time_kernel(lambda: K.head_linear(o_lat, uv, None), flush=flush), 2.0 * T * H * R * V)
+    # (K is one head's 128 to 192 elements: the operands' bytes, not the products, set these kernels' floor)
+    for name, nbytes in (("head_linear_absorb", T * H * (D + R) * 2 + H * R * D * 2), ("head_linear_values", T * H * (R + V) * 2 + H * R * V * 2)):
+        out["kernels"][name]["frac_hbm"] = round(nbytes / (out["kernels"][name]["ms"] / 1e3) / bw, 3)
 
     def latent_case(q_len, ctx, seqs):
         n = seqs * (ctx // 16)

@@ -110,6 +110,10 @@ struct GemmParams {
     const int* tile_group;         // [m_tiles] or nullptr
     const int* tile_rows;          // [m_tiles * (RV_PAIR ? 2 : 1)]
     const int* tile_order;         // [m_tiles * n_tiles]
+    // A grouped product may also read every group's K elements from its own columns of x (x rows hold the groups side
+    // by side, a_group_k elements apart: the heads of an attention layer) and write every group's N results into its
+    // own columns of wider output rows (row stride ldc, group g from column g * c_group).  Plain epilogue only.
+    int a_group_k, c_group, ldc;   // 0, 0, 0: one K range for all groups, rows of N results
 };
 
 // (unit, column tile) of entry `tile` of the work; false: nothing to do there
@@ -315,6 +319,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (m0 < 0) m0 = __ldg(rows);                                   // no block of its own: the partner's again
                 }
                 const int w_base = grp * p.N;                                       // the group's first row of W
+                const int a_k0 = grp * p.a_group_k;                                 // ... and first column of x
                 for (int kb = kb_first; kb < kb_last; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, &abort_flag, 1)) { ok = false; break; }
                     const uint32_t a_dst = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
@@ -326,7 +331,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         const int w0 = w_base + (gated ? (rank == 0 ? nt * (BN / 2) : half_n + nt * (BN / 2)) : nt * BN + (int)rank * (BN / 2));
                         const uint32_t bar = pair_map(full0 + 8 * stage, 0);
                         if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * STAGE_BYTES);
-                        tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, bar);
+                        tma_load_2d_pair(a_dst, &map_a, a_k0 + kb * BK, m0, bar);
                         tma_load_2d_pair(b_dst, &map_b, kb * BK, w0, bar);
                         ++issued;
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -334,7 +339,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                     const uint32_t bar = full0 + 8 * stage;
                     mbar_expect_tx(bar, STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, kb * BK, m0, bar);
+                    tma_load_2d(a_dst, &map_a, a_k0 + kb * BK, m0, bar);
                     if (gated) {       // 128 gate rows, then the 128 up rows of the same columns
                         tma_load_2d(b_dst, &map_b, kb * BK, w_base + nt * (BN / 2), bar);
                         tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, kb * BK, w_base + half_n + nt * (BN / 2), bar);
@@ -554,15 +559,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             } else {
                 const int n0 = nt * BN;
+                // (rows of ldc elements, the group's results from column coff on; without these options ldc = N, coff = 0)
+                const int ldc = p.ldc ? p.ldc : p.N;
+                const int coff = p.c_group ? __ldg(p.tile_group + unit) * p.c_group : 0;
+                const bool wide_ok = ((ldc | coff) & 7) == 0;
                 for (int c = c_begin; c < c_end; c += 32) {
                     if (n0 + c >= p.N) break;              // uniform over the warp
                     uint32_t r[32];
                     load_acc(c, r);
                     if (m < p.M) {
                         const int n = n0 + c;
-                        const bool vec = n + 32 <= p.N && (p.N & 7) == 0;
+                        const bool vec = n + 32 <= p.N && (p.N & 7) == 0 && wide_ok;
                         if (vec && !p.out_f32) {
-                            __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.N + n;
+                            __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * ldc + coff + n;
                             const __nv_bfloat16* res = p.residual ? p.residual + (size_t)m * p.N + n : nullptr;
 #pragma unroll
                             for (int v = 0; v < 4; ++v) {
@@ -580,7 +589,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 *reinterpret_cast<uint4*>(dst + v * 8) = o;
                             }
                         } else if (vec && p.out_f32 && !p.residual && (p.N & 3) == 0) {
-                            float4* dst = reinterpret_cast<float4*>((float*)p.out + (size_t)m * p.N + n);
+                            float4* dst = reinterpret_cast<float4*>((float*)p.out + (size_t)m * ldc + coff + n);
 #pragma unroll
                             for (int v = 0; v < 8; ++v)
                                 dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
@@ -591,8 +600,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 if (n + e >= p.N) continue;
                                 float val = __uint_as_float(r[e]);
                                 if (p.residual) val += __bfloat162float(p.residual[(size_t)m * p.N + n + e]);
-                                if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n + e] = val;
-                                else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n + e] = __float2bfloat16_rn(val);
+                                if (p.out_f32) ((float*)p.out)[(size_t)m * ldc + coff + n + e] = val;
+                                else ((__nv_bfloat16*)p.out)[(size_t)m * ldc + coff + n + e] = __float2bfloat16_rn(val);
                             }
                         }
                     }
@@ -703,28 +712,48 @@ RV_EXPORT int rv_gemm_tcgen05_column_tiles(int N, int epilogue) {
 RV_EXPORT int rv_gemm_tcgen05_block_rows() { return BM; }
 RV_EXPORT int rv_gemm_tcgen05_ranks() { return RV_PAIR ? 2 : 1; }
 
-RV_EXPORT int rv_gemm_tcgen05_grouped(const void* x, const void* w, const int* tile_group, const int* tile_rows, const int* tile_order,
-                                      void* out, int out_f32, int M, int N, int K, int groups, int units, int epilogue, int* status,
-                                      cudaStream_t stream) {
+static int grouped_launch(const void* x, const void* w, const int* tile_group, const int* tile_rows, const int* tile_order,
+                          void* out, int out_f32, int M, int N, int K, int groups, int units, int epilogue, int x_cols, int a_group_k,
+                          int c_group, int ldc, int* status, cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0 || groups <= 0 || units <= 0 || units > 32767 || !tile_group || !tile_rows || !tile_order) return RV_ERR_BAD_SIZE;
     if (epilogue != EPI_PLAIN && epilogue != EPI_GATED) return RV_ERR_UNSUPPORTED;
-    if (K % 8 || M % BM) return RV_ERR_UNSUPPORTED;
+    if (K % 8 || x_cols % 8 || a_group_k % 8) return RV_ERR_UNSUPPORTED;       // TMA rows and column origins on 16-byte boundaries
+    if ((a_group_k || c_group || ldc) && epilogue != EPI_PLAIN) return RV_ERR_UNSUPPORTED;
     if (epilogue == EPI_GATED && (N & 1)) return RV_ERR_BAD_SIZE;
     if ((long long)groups * N > 0x7fffffffLL) return RV_ERR_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16) return RV_ERR_ALIGNMENT;
     if (M == 0) return RV_OK;
     alignas(64) CUtensorMap map_a, map_b;
-    int st = rv_make_bf16_map(&map_a, x, M, K, BM);
+    int st = rv_make_bf16_map(&map_a, x, M, x_cols, BM);
     if (st != RV_OK) return st;
     st = rv_make_bf16_map(&map_b, w, groups * N, K, BN / 2);
     if (st != RV_OK) return st;
     GemmParams p = {};
     p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
     p.splits = 1; p.tile_group = tile_group; p.tile_rows = tile_rows; p.tile_order = tile_order;
+    p.a_group_k = a_group_k; p.c_group = c_group; p.ldc = ldc;
     p.m_tiles = units;
     p.n_tiles = rv_gemm_tcgen05_column_tiles(N, epilogue);
     if (p.n_tiles > 65535) return RV_ERR_BAD_SIZE;
     return launch_gemm(map_a, map_b, p, 0, stream);
+}
+
+RV_EXPORT int rv_gemm_tcgen05_grouped(const void* x, const void* w, const int* tile_group, const int* tile_rows, const int* tile_order,
+                                      void* out, int out_f32, int M, int N, int K, int groups, int units, int epilogue, int* status,
+                                      cudaStream_t stream) {
+    return grouped_launch(x, w, tile_group, tile_rows, tile_order, out, out_f32, M, N, K, groups, units, epilogue, K, 0, 0, 0, status, stream);
+}
+
+// out[m, g * c_group + n] = sum_k x[m, g * a_group_k + k] w[g * N + n, k] for the rows that the work units name: x has rows
+// of x_cols elements that hold the groups' K elements side by side, out rows of ldc elements.  Plain epilogue.
+// (Where K is no multiple of the k block, the columns of x that follow a group's meet zeros: W is read beyond its K.)
+RV_EXPORT int rv_gemm_tcgen05_batched(const void* x, const void* w, const int* tile_group, const int* tile_rows, const int* tile_order,
+                                      void* out, int out_f32, int M, int N, int K, int groups, int units, int x_cols, int a_group_k,
+                                      int c_group, int ldc, int* status, cudaStream_t stream) {
+    if (x_cols <= 0 || a_group_k <= 0 || c_group <= 0 || ldc <= 0) return RV_ERR_BAD_SIZE;
+    if ((long long)(groups - 1) * a_group_k + K > x_cols || (long long)(groups - 1) * c_group + N > ldc) return RV_ERR_BAD_SIZE;
+    return grouped_launch(x, w, tile_group, tile_rows, tile_order, out, out_f32, M, N, K, groups, units, EPI_PLAIN, x_cols, a_group_k,
+                          c_group, ldc, status, stream);
 }
 
 // The q/k/v product of an attention layer for many rows, with bias, rotation and the cache write in

@@ -1087,12 +1087,59 @@ class CudaKernels:
             out = torch.empty((T, H, N), dtype=out_dtype or x.dtype, device=x.device)
         if tuple(out.shape) != (T, H, N) or out.stride(2) != 1:
             raise KernelError(f"head_linear: out of shape {tuple(out.shape)} and strides {out.stride()}, expected {(T, H, N)}")
+        if self._head_linear_tcgen05(x, weight, out):
+            return out
         st = self._lib("latent.cu").rv_head_linear(
             _ptr(x), c_int(self._dt(x, "x")), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)), _ptr(weight),
             c_int(self._dt(weight, "weight")), _ptr(out), c_int(self._dt(out, "out")), ctypes.c_longlong(out.stride(0)),
             ctypes.c_longlong(out.stride(1)), c_int(T), c_int(H), c_int(N), c_int(K), self._stream())
         _check("head_linear", st)
         return out
+
+    HEAD_LINEAR_TCGEN05_MIN_ROWS = 128      # rows from which the per-head products run on the tcgen05 GEMM (batched over the heads)
+
+    def _head_work(self, lib, T: int, H: int, N: int):
+        """The work units of a per-head product of T rows on the device (made once per shape): every head's blocks of 128
+        rows in pairs (the CTAs of a tile), and the order head by head, column tile by column tile, the head's units."""
+        key = (T, H, N)
+        cache = self.__dict__.setdefault("_head_work_cache", {})
+        if key not in cache:
+            if len(cache) > 64:
+                cache.clear()
+            R, ranks = int(lib.rv_gemm_tcgen05_block_rows()), int(lib.rv_gemm_tcgen05_ranks())
+            nt = int(lib.rv_gemm_tcgen05_column_tiles(c_int(N), c_int(0)))
+            blocks = -(-T // R)
+            per_head = -(-blocks // ranks)
+            group, rows, order = [], [], []
+            for h in range(H):
+                for u in range(per_head):
+                    group.append(h)
+                    rows.extend((u * ranks + r) * R if u * ranks + r < blocks else -1 for r in range(ranks))
+                order.extend(((h * per_head + u) << 16) | t for t in range(nt) for u in range(per_head))
+            as_dev = lambda v: torch.tensor(v, dtype=torch.int32).to(self.device)
+            cache[key] = (as_dev(group), as_dev(rows), as_dev(order), H * per_head)
+        return cache[key]
+
+    def _head_linear_tcgen05(self, x, weight, out) -> bool:
+        """`head_linear` on the tcgen05 GEMM where the operands allow: bfloat16, many rows, rows and head slices of x on
+        16-byte boundaries.  A head is a group of the grouped product: its K elements are columns of x, its results
+        columns of out.  False: not taken."""
+        H, N, K = weight.shape
+        T = x.shape[0]
+        if not (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+                and T >= self.HEAD_LINEAR_TCGEN05_MIN_ROWS and K % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+                and x.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and x.stride(1) >= K and x.stride(0) >= (H - 1) * x.stride(1) + K
+                and out.stride(0) >= (H - 1) * out.stride(1) + N and out.stride(1) >= N and H * (-(-T // 128)) <= 32767
+                and not torch.cuda.is_current_stream_capturing()):
+            return False
+        lib = self._lib("gemm_tcgen05.cu", ("-DRV_PAIR=1",))
+        group, rows, order, units = self._head_work(lib, T, H, N)
+        st = lib.rv_gemm_tcgen05_batched(
+            _ptr(x), _ptr(weight), _ptr(group), _ptr(rows), _ptr(order), _ptr(out), c_int(1 if out.dtype == torch.float32 else 0),
+            c_int(T), c_int(N), c_int(K), c_int(H), c_int(units), c_int(x.stride(0)), c_int(x.stride(1)), c_int(out.stride(1)),
+            c_int(out.stride(0)), _ptr(self._status), self._stream())
+        _check("gemm_tcgen05_batched", st)
+        return True
 
     def latent_attention(self, q_row, cache_layer, meta: AttentionMeta, num_heads: int, row: int, value_dim: int, scale: float,
                          gate: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -90,9 +90,12 @@ def test_latent_prepare(K, dtype, H, D, Rd, dims, R):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,H,N,K_", [(1, 3, 40, 24), (70, 4, 128, 64), (130, 2, 20, 9), (33, 5, 13, 10), (257, 4, 80, 128)])
+@pytest.mark.parametrize("T,H,N,K_", [(1, 3, 40, 24), (70, 4, 128, 64), (130, 2, 20, 9), (33, 5, 13, 10), (257, 4, 80, 128),
+                                       (300, 9, 192, 72), (1030, 3, 264, 200), (128, 2, 16, 8)])
 def test_per_head_products(K, dtype, T, H, N, K_):
-    """Contiguous and sliced operands; bfloat16 with aligned rows takes the tensor-core kernel, the rest the plain one."""
+    """Contiguous and sliced operands.  bfloat16 with aligned rows: the tcgen05 GEMM batched over the heads from 128 rows on
+    (K that is no multiple of its k block, more columns than a tile, an odd number of row blocks per head), mma.sync below;
+    everything else the plain kernel."""
     x, w = rnd(T, H, K_, seed=12).to(dtype), rnd(H, N, K_, seed=13, scale=0.3).to(dtype)
     want = torch.einsum("thk,hnk->thn", x.double(), w.double())
     got = K.head_linear(x.cuda(), w.cuda(), None, out_dtype=torch.float32)
@@ -102,6 +105,7 @@ def test_per_head_products(K, dtype, T, H, N, K_):
     wide_out = torch.full((T, H, N + 16), 5.0, dtype=dtype).cuda()
     K.head_linear(wide_in[:, :, :K_], w.cuda(), wide_out[:, :, :N])
     assert rel_err(wide_out[:, :, :N], want) < TOL[dtype] / 2 and bool((wide_out[:, :, N:] == 5.0).all())
+    K.raise_on_abort()
 
 
 # ---------------------------------------------------------------------------------------- attention over cached rows
