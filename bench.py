@@ -662,6 +662,7 @@ def run_vipelix(args):
                                "decode_ratio": round(a["decode_tok_s"] / b["decode_tok_s"], 3)}
 
     # ---- the design's kernels alone, at the "4k" sizes, beside the like kernel of the Llama path ------------------
+    torch.manual_seed(0)           # (which experts the tokens of the expert cases choose)
     z = VIPELIX_SIZES["4k"]
     dev, bf = "cuda", torch.bfloat16
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
