@@ -29,7 +29,7 @@ def rnd(*shape, seed=0, scale=1.0):
 
 # ---------------------------------------------------------------------------------------- row kernels
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("cols", [44, 320, 4096 + 24])
+@pytest.mark.parametrize("cols", [44, 352, 4096 + 24])
 def test_add_then_norm_for_the_next_sublayer(K, dtype, cols):
     y, r = rnd(6, cols, seed=1, scale=3.0), rnd(6, cols, seed=2)
     g1, g2 = (rnd(cols, seed=3) + 1.0).to(dtype), (rnd(cols, seed=4) + 1.0).to(dtype)
@@ -60,7 +60,7 @@ def test_stream_add_polynorm_softcap(K, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,D,Rd,dims,R", [(3, 24, 16, 16, 40), (4, 8, 12, 8, 20), (1, 9, 6, 6, 35), (4, 64, 32, 32, 128), (5, 10, 2, 2, 13)])
+@pytest.mark.parametrize("H,D,Rd,dims,R", [(3, 24, 16, 16, 40), (4, 8, 12, 8, 20), (1, 9, 6, 6, 35), (6, 48, 32, 32, 112), (5, 10, 2, 2, 13)])
 def test_latent_prepare(K, dtype, H, D, Rd, dims, R):
     T, page, n_pages, eps, base = 11, 8, 5, 1e-5, 300.0
     row = R + Rd
@@ -149,7 +149,7 @@ def plain_latent(q, rows_per_seq, q_lens, vd, scale, gate):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,row,vd,page", [(4, 160, 128, 16), (3, 56, 40, 8), (2, 128, 96, 16), (5, 64, 48, 32), (1, 300, 260, 16)])
+@pytest.mark.parametrize("H,row,vd,page", [(6, 144, 112, 16), (3, 56, 40, 8), (2, 128, 96, 16), (5, 64, 48, 32), (1, 300, 260, 16)])
 @pytest.mark.parametrize("q_lens,ctx", [((1, 1, 1), (257, 64, 1)), ((70, 5), (70, 133)), ((1, 40, 1, 2), (100, 300, 17, 2))])
 def test_latent_attention_kernels(K, dtype, H, row, vd, page, q_lens, ctx):
     """Decoded tokens alone (key splits), prompt portions behind a prefix, and both in one step; rows of the sizes
@@ -193,8 +193,8 @@ def test_one_far_key_takes_all_the_weight(K, dtype, far):
 
 # ---------------------------------------------------------------------------------------- experts
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,width,ff,E,top,ids", [(1, 48, 24, 5, 2, 37), (9, 44, 9, 4, 4, 37), (70, 320, 96, 16, 2, 37), (300, 64, 40, 3, 1, 37),
-                                                   (513, 320, 96, 16, 2, 200), (200, 128, 264, 7, 3, 2), (1100, 256, 128, 40, 4, 1)])
+@pytest.mark.parametrize("T,width,ff,E,top,ids", [(1, 48, 24, 5, 2, 37), (9, 44, 9, 4, 4, 37), (70, 384, 88, 12, 2, 37), (300, 64, 40, 3, 1, 37),
+                                                   (513, 384, 88, 12, 3, 200), (200, 128, 264, 7, 3, 2), (1100, 256, 128, 40, 4, 1)])
 def test_experts_chosen_by_table(K, dtype, T, width, ff, E, top, ids):
     """Few tokens (a kernel that streams the chosen experts' weights) and many (sorted by expert, grouped products on the
     tensor cores, in bfloat16); with two or one token id in play most experts get no row at all and one gets many tiles."""
