@@ -30,14 +30,34 @@
 //
 // Rule as in attention_flash.cu (v3/kernels/paged_attention_sm89.cu:277-308 of the reference):
 // token i of the step's q_len tokens sits at p = ctx_len - q_len + i and sees keys (p - window, p].
-// Cache layer layout: [num_pages, 2 (k, v), nkv, page_size, HEAD_DIM].
+// Cache layer layout: [num_pages, 2 (k, v), nkv, page_size, HEAD_DIM] (one plane in a LATENT_ROW build, see below).
 #include "common.cuh"
 #include "tcgen05.cuh"
 
+// A second kind of build, -DLATENT_ROW=r -DV_DIM=v, serves mixers that keep ONE row of r elements per token and kv head,
+// read as the key in full and as the value in its leading v elements (latent attention: all heads of a token are a group
+// on one such row).  The cache layer is then [num_pages, 1, nkv, page_size, r]; keys are fetched in slabs of 64 elements
+// up to the next multiple of 64 (what lies beyond r is filled with zeros by the copy), values as the leading slabs of the
+// same rows; O has v columns of tensor memory behind the two S buffers.  r up to 256 (a multiple of 8), v a multiple of
+// 32 up to r.  With r beyond 128 or v beyond 128 one CTA fits an SM instead of two.
+#ifdef LATENT_ROW
+#ifndef V_DIM
+#error "a LATENT_ROW build needs V_DIM"
+#endif
+#define ROW_REAL LATENT_ROW
+#define HEAD_DIM (((LATENT_ROW + 63) / 64) * 64)
+#define KV_PLANES 1
+static_assert(LATENT_ROW % 8 == 0 && LATENT_ROW >= 32 && LATENT_ROW <= 256, "a cached row is a multiple of 8 up to 256 elements");
+static_assert(V_DIM % 32 == 0 && V_DIM >= 32 && V_DIM <= LATENT_ROW, "the value is a multiple of 32 elements at the start of the row");
+#else
 #ifndef HEAD_DIM
 #define HEAD_DIM 128
 #endif
 static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "this kernel is built for head sizes 64 and 128");
+#define ROW_REAL HEAD_DIM
+#define V_DIM HEAD_DIM
+#define KV_PLANES 2
+#endif
 
 #define ROWS 128
 #define KV_TILE 64
@@ -46,20 +66,27 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "this kernel is built for head 
 #define VLOADER_WARP (SOFTMAX_WARPS + 1)       // the values
 #define QK_WARP (SOFTMAX_WARPS + 2)            // issues S = Q K^T
 #define PV_WARP (SOFTMAX_WARPS + 3)            // issues O += P V
-#define HALVES (HEAD_DIM / 64)                 // 64-element (128-byte) slabs of the head dimension
+#define HALVES (HEAD_DIM / 64)                 // 64-element (128-byte) slabs of the head dimension (keys and queries)
+#define V_HALVES ((V_DIM + 63) / 64)           // ... of the values
 #define Q_BYTES (ROWS * HEAD_DIM * 2)
-#define KV_BYTES (KV_TILE * HEAD_DIM * 2)      // one of K or V for a tile
+#define K_BYTES (KV_TILE * HEAD_DIM * 2)       // the keys of a tile
+#define V_BYTES (KV_TILE * V_HALVES * 128)     // the values of a tile
 #define NUM_THREADS (32 * (SOFTMAX_WARPS + 4)) // two warpgroups: the softmax warps; 2 loader warps and 2 MMA warps
 // Two CTAs fit an SM, so a thread starts with 128 registers; the four warps that load and issue give
 // most of theirs back and the softmax warps take them (setmaxnreg works on whole warpgroups).
 #define REGS_SOFTMAX 200
 #define REGS_OTHERS 56
-#define TMEM_COLS 256
+#define TMEM_COLS (128 + V_DIM <= 256 ? 256 : 512)
 #define S_COL 0                   // two S buffers of 64 columns; P (bf16 pairs) reuses the first 32 columns of each
 #define O_COL 128
-// Stages of the key ring and of the value ring: what fits beside Q with two CTAs on an SM.
+// Stages of the key ring and of the value ring: what fits beside Q with two CTAs on an SM (one where the rows are long).
+#ifdef LATENT_ROW
+#define NK (HEAD_DIM >= 256 ? 2 : 3)
+#define NV 2
+#else
 #define NK (HEAD_DIM == 128 ? 3 : 4)
 #define NV (HEAD_DIM == 128 ? 2 : 4)
+#endif
 // mbarriers, by their index
 #define B_Q 0
 #define B_K 1                      // keys of a stage have landed [NK]
@@ -156,8 +183,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* q_s = smem_raw;                           // [HALVES][128 rows x 128 B]
     unsigned char* k_s = q_s + Q_BYTES;                      // [NK stages][HALVES][KV_TILE keys x 128 B]
-    unsigned char* v_s = k_s + NK * KV_BYTES;                // [NV stages][HALVES][KV_TILE keys x 128 B]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + NV * KV_BYTES);
+    unsigned char* v_s = k_s + NK * K_BYTES;                 // [NV stages][V_HALVES][KV_TILE keys x 128 B]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + NV * V_BYTES);
     uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 30);
     volatile int& abort_flag = *reinterpret_cast<volatile int*>(bars + 31);
 
@@ -213,7 +240,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
     // value tiles start as zeros: a page that is not loaded (beyond the context, or given back by
     // a window) must not meet a probability of zero with a NaN
-    for (int i = tid; i < NV * KV_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < NV * V_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
     // ... and so do the query rows that the box of whole tokens leaves over (a row is 128 bytes in
     // each half of the head, whatever the swizzle does inside it)
     for (int i = tid; i < (ROWS - tile_rows) * 8 * HALVES; i += NUM_THREADS) {
@@ -246,6 +273,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_OTHERS));
         const int which = warp == LOADER_WARP ? 0 : 1;
         const int stages = which == 0 ? NK : NV;
+        const int halves = which == 0 ? HALVES : V_HALVES;                   // slabs of 64 elements that this loader fetches of a row
+        const uint32_t stage_bytes = which == 0 ? K_BYTES : V_BYTES;
         const uint32_t bar_full0 = which == 0 ? bar_k0 : bar_v0, bar_free0 = which == 0 ? bar_kfree0 : bar_vfree0;
         const uint32_t ring = smem_u32(which == 0 ? k_s : v_s);
         auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
@@ -259,22 +288,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         };
         auto issue = [&](int t, int stage, int page) {
             const uint32_t bar = bar_full0 + 8 * stage;
-            const uint32_t dst0 = ring + (uint32_t)stage * KV_BYTES;
+            const uint32_t dst0 = ring + (uint32_t)stage * stage_bytes;
             const int key = t * KV_TILE + lane * box_keys;
             const unsigned mask = __ballot_sync(0xffffffffu, page >= 0);
-            if (lane == 0) mbar_expect_tx(bar, (uint32_t)__popc(mask) * HALVES * (uint32_t)box_keys * 128u);
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)__popc(mask) * (uint32_t)halves * (uint32_t)box_keys * 128u);
             __syncwarp();
             if (page >= 0) {
-                const int row = ((page * 2 + which) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
+                // (one plane: the values are the leading slabs of the rows that hold the keys)
+                const int row = ((page * KV_PLANES + (KV_PLANES == 2 ? which : 0)) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
 #pragma unroll
-                for (int h = 0; h < HALVES; ++h)
+                for (int h = 0; h < halves; ++h)
                     tma_load_2d(dst0 + (uint32_t)h * (KV_TILE * 128) + (uint32_t)lane * box_keys * 128, &map_kv, h * 64, row, bar);
             }
             __syncwarp();
         };
         // Q: one box of [64 hd, G heads, floor(128 / G) tokens] per half of the head dimension
         if (which == 0 && lane == 0) {
-            mbar_expect_tx(bar_q, (uint32_t)tile_rows * HEAD_DIM * 2);
+            mbar_expect_tx(bar_q, (uint32_t)tile_rows * HEAD_DIM * 2);       // (whole boxes count, also where they reach beyond the row)
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(smem_u32(q_s) + h * (ROWS * 128), &map_q, h * 64, kvh * G, q_start + row0 / G, bar_q);
@@ -331,7 +361,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
                     const uint64_t dq = umma_desc(smem_u32(q_s) + h * (ROWS * 128));
-                    const uint64_t dk = umma_desc(smem_u32(k_s) + k_stage * KV_BYTES + h * (KV_TILE * 128));
+                    const uint64_t dk = umma_desc(smem_u32(k_s) + k_stage * K_BYTES + h * (KV_TILE * 128));
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         tcgen05_mma_bf16(tmem_base + S_COL + buf * KV_TILE, dq + (uint64_t)(2 * j), dk + (uint64_t)(2 * j),
@@ -349,7 +379,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // ------------------------------------------------------------ second MMA warp: O += P V
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_OTHERS));
         if (lane == 0) {
-            const uint32_t idesc_o = umma_idesc_bf16(ROWS, HEAD_DIM) | (1u << 16);       // B is MN-major
+            const uint32_t idesc_o = umma_idesc_bf16(ROWS, V_DIM) | (1u << 16);          // B is MN-major
             bool ok = true;
             int v_stage = 0;
             uint32_t v_phase = 0;
@@ -370,7 +400,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (trm) p.status[8 + 2400 + (it - tr0) * 5 + 2] = (int)clock64();
 #endif
                 const uint32_t tp = tmem_base + S_COL + b * KV_TILE;     // P(it): bf16 pairs in the first half of S buffer b
-                const uint64_t dv = umma_desc_mn(smem_u32(v_s) + v_stage * KV_BYTES, KV_TILE * 128);
+                const uint64_t dv = umma_desc_mn(smem_u32(v_s) + v_stage * V_BYTES, KV_TILE * 128);
 #pragma unroll
                 for (int j = 0; j < KV_TILE / 16; ++j)   // 16 keys per MMA: 8 columns along P's rows, 2048 bytes down V
                     tcgen05_mma_bf16_ts(tmem_base + O_COL, tp + 8 * j, dv + (uint64_t)(128 * j), idesc_o, (it | j) != 0);
@@ -468,7 +498,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (!mbar_wait(bar_o_full0 + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, &abort_flag, 11)) { ok = false; break; }
                 tcgen05_fence_after();
 #pragma unroll
-                for (int c = 0; c < HEAD_DIM; c += 32) {
+                for (int c = 0; c < V_DIM; c += 32) {
                     uint32_t o[32];
                     tmem_ld_32x32(t_lane + O_COL + c, o);
                     tmem_ld_wait();
@@ -521,9 +551,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 float inv = den > 0.f ? num / den : 0.f;
                 if (p.gate && in_range) inv *= p.gate[(size_t)(q_start + tok_i) * p.nh + head];
-                __nv_bfloat16* dst = p.out + ((size_t)(q_start + tok_i) * p.nh + head) * HEAD_DIM;
+                __nv_bfloat16* dst = p.out + ((size_t)(q_start + tok_i) * p.nh + head) * V_DIM;
 #pragma unroll
-                for (int c = 0; c < HEAD_DIM; c += 32) {
+                for (int c = 0; c < V_DIM; c += 32) {
                     uint32_t o[32];
                     tmem_ld_32x32(t_lane + O_COL + c, o);
                     tmem_ld_wait();
@@ -574,8 +604,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 static int make_q_map(CUtensorMap* map, const void* q, int n_tokens, int nh, int G) {
     RvEncodeTiledFn fn = rv_encode_fn();
     if (!fn) return RV_ERR_UNSUPPORTED;
-    const cuuint64_t dims[3] = {HEAD_DIM, (cuuint64_t)nh, (cuuint64_t)n_tokens};
-    const cuuint64_t strides[2] = {HEAD_DIM * 2, (cuuint64_t)nh * HEAD_DIM * 2};
+    const cuuint64_t dims[3] = {ROW_REAL, (cuuint64_t)nh, (cuuint64_t)n_tokens};
+    const cuuint64_t strides[2] = {ROW_REAL * 2, (cuuint64_t)nh * ROW_REAL * 2};
     const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(ROWS / G)};
     const cuuint32_t elem[3] = {1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
@@ -584,7 +614,9 @@ static int make_q_map(CUtensorMap* map, const void* q, int n_tokens, int nh, int
     return r == CUDA_SUCCESS ? RV_OK : RV_ERR_BAD_SIZE;
 }
 
-RV_EXPORT int rv_attention_tcgen05_head_dim() { return HEAD_DIM; }
+RV_EXPORT int rv_attention_tcgen05_head_dim() { return ROW_REAL; }
+RV_EXPORT int rv_attention_tcgen05_value_dim() { return V_DIM; }
+RV_EXPORT int rv_attention_tcgen05_planes() { return KV_PLANES; }
 
 // Attention of the sequences that bring more than one token to the step (the others are left to
 // the decode kernel).  Refuses (RV_ERR_UNSUPPORTED) what it is not built for: a head size other
@@ -596,7 +628,7 @@ RV_EXPORT int rv_attention_tcgen05_ex(const void* q, const void* cache, long lon
                                       int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window,
                                       int max_q_len, int* status, float softcap, const float* sinks, const float* gate,
                                       cudaStream_t stream) {
-    if (hd != HEAD_DIM) return RV_ERR_UNSUPPORTED;
+    if (hd != ROW_REAL) return RV_ERR_UNSUPPORTED;
     if (n_tokens < 0 || num_seqs < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 || max_q_len <= 0)
         return RV_ERR_BAD_SIZE;
     const int G = nh / nkv;
@@ -609,7 +641,7 @@ RV_EXPORT int rv_attention_tcgen05_ex(const void* q, const void* cache, long lon
     alignas(64) CUtensorMap map_q, map_kv;
     int st = make_q_map(&map_q, q, n_tokens, nh, G);
     if (st != RV_OK) return st;
-    st = rv_make_bf16_map(&map_kv, cache, num_pages * 2 * nkv * page_size, HEAD_DIM, page_size < KV_TILE ? page_size : KV_TILE);
+    st = rv_make_bf16_map(&map_kv, cache, num_pages * KV_PLANES * nkv * page_size, ROW_REAL, page_size < KV_TILE ? page_size : KV_TILE);
     if (st != RV_OK) return st;
     AttnParams p;
     p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.ctx_lens = ctx_lens; p.out = (__nv_bfloat16*)out;
@@ -621,7 +653,7 @@ RV_EXPORT int rv_attention_tcgen05_ex(const void* q, const void* cache, long lon
     p.cap_log2e = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
     p.sinks = sinks; p.gate = gate;
-    const int smem = Q_BYTES + (NK + NV) * KV_BYTES + 256;
+    const int smem = Q_BYTES + NK * K_BYTES + NV * V_BYTES + 256;
     static RvPerDevice configured;
     if (int e = rv_configure_smem(configured, attention_tcgen05_kernel, smem)) return e;
     const int tile_tokens = ROWS / G;

@@ -95,6 +95,7 @@ class CudaKernels:
     BALANCED_DECODE = True  # decode attention by the kernel that cuts all tiles evenly over resident CTAs ...
     BALANCED_MIN_PAIRS = 256  # ... from this many (sequence, kv head) pairs on
     LATENT_FLASH = True       # latent attention in bfloat16 runs on the tensor-core flash kernel where its sizes allow (else the plain kernel)
+    LATENT_TCGEN05 = True     # ... and its prompt portions on the tcgen05 kernel's one-plane build (rows up to 256, values a multiple of 32)
     FUSED_QKV_PREFILL = True  # from TCGEN05_MIN_ROWS rows on the prefill GEMM rotates and writes the cache in its epilogue
     FUSED_NORM_MAX_ROWS = 0 # rows up to which an RMSNorm is applied inside the decode GEMM that consumes it
     FUSED_QKV_MAX_ROWS = 64 # rows up to which q/k/v product, rotation and cache write are one kernel
@@ -437,11 +438,16 @@ class CudaKernels:
         return out
 
     def attention_tcgen05(self, q, cache_layer, meta, out, num_heads, num_kv_heads, head_dim, scale, window, status=None,
-                          softcap=None, sinks=None, gate=None):
+                          softcap=None, sinks=None, gate=None, value_dim=None):
         """The tcgen05 flash-attention kernel for the sequences of a step that bring more than one
-        token (bfloat16, head size 64 or 128, groups of up to 128 heads, pages of at least 8 keys)."""
-        _need(q, "q", torch.bfloat16, 2); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
-        lib = self._lib("attention_tcgen05.cu", (f"-DHEAD_DIM={head_dim}",))
+        token (bfloat16, head size 64 or 128, groups of up to 128 heads, pages of at least 8 keys).
+        `value_dim`: the build for one-plane caches (rows of `head_dim` elements, up to 256, that are keys in full and
+        values in their leading `value_dim` elements, a multiple of 32); `out` then has rows of that width."""
+        _need(q, "q", torch.bfloat16); _need(cache_layer, "cache_layer", torch.bfloat16, 5)
+        defines = (f"-DHEAD_DIM={head_dim}",) if value_dim is None else (f"-DLATENT_ROW={head_dim}", f"-DV_DIM={value_dim}")
+        if cache_layer.shape[1] != (2 if value_dim is None else 1):
+            raise KernelError(f"attention_tcgen05: a cache layer of {cache_layer.shape[1]} planes for a kernel of {2 if value_dim is None else 1}")
+        lib = self._lib("attention_tcgen05.cu", defines)
         st = lib.rv_attention_tcgen05_ex(
             _ptr(q), _ptr(cache_layer), ctypes.c_longlong(cache_layer.shape[0]), _ptr(meta.block_tables),
             _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(out), c_int(q.shape[0]), c_int(meta.num_seqs),
@@ -1157,8 +1163,19 @@ class CudaKernels:
         self._check_attention_extras(q_row.view(T, -1), num_heads, None, gate)
         out = torch.empty((T, num_heads, value_dim), dtype=q_row.dtype, device=q_row.device)
         page = cache_layer.shape[3]
-        if self.LATENT_FLASH and q_row.dtype == torch.bfloat16 and row % 16 == 0 and value_dim % 16 == 0 and row <= 256 \
-                and not (page & (page - 1)):
+        flash_ok = (self.LATENT_FLASH and q_row.dtype == torch.bfloat16 and row % 16 == 0 and value_dim % 16 == 0 and row <= 256
+                    and not (page & (page - 1)))
+        if (self.LATENT_TCGEN05 and self.TCGEN05_ATTENTION and q_row.dtype == torch.bfloat16 and row % 8 == 0 and 32 <= row <= 256
+                and value_dim % 32 == 0 and num_heads <= 128 and page >= 8 and not (page & (page - 1))
+                and meta.max_q_len >= self.TCGEN05_ATTENTION_MIN_TOKENS and (flash_ok or meta.num_decode == 0)):
+            # prompt portions on the tcgen05 kernel (all heads of a token side by side in a tile of 128 rows); the step's
+            # one-token sequences, which it leaves alone, on the decode tiling of the mma.sync kernel
+            self.attention_tcgen05(q_row, cache_layer, meta, out, num_heads, 1, row, scale, None, gate=gate, value_dim=value_dim)
+            if meta.num_decode:
+                self.flash_attention(q_row, cache_layer, meta, out, num_heads, 1, row, scale, None, mode=1, q_filter=1, max_q_len=1,
+                                     gate=gate, value_dim=value_dim)
+            return out
+        if flash_ok:
             # the tensor-core kernel: all heads of a token are rows of one tile over the token's single "kv head"
             args = (q_row, cache_layer, meta, out, num_heads, 1, row, scale, None)
             if meta.max_q_len == 1:

@@ -21,6 +21,7 @@ def all_variants() -> List[Tuple[str, Sequence[str]]]:
             out.extend((src, (f"-DHEAD_DIM={row}", f"-DV_DIM={vd}", "-DKV_PLANES=1")) for row, vd in FLASH_LATENT_ROWS)
         elif src == "attention_tcgen05.cu":
             out.extend((src, (f"-DHEAD_DIM={hd}",)) for hd in (64, 128))
+            out.extend((src, (f"-DLATENT_ROW={row}", f"-DV_DIM={vd}")) for row, vd in FLASH_LATENT_ROWS)
         elif src == "gemm_tcgen05.cu":
             # one CTA per tile and pairs of CTAs, each with tiles of 256 and of 128 columns
             out.extend([(src, ()), (src, ("-DRV_PAIR=1",)), (src, ("-DBN=128",)), (src, ("-DRV_PAIR=1", "-DBN=128"))])

@@ -149,11 +149,13 @@ def plain_latent(q, rows_per_seq, q_lens, vd, scale, gate):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,row,vd,page", [(6, 144, 112, 16), (3, 56, 40, 8), (2, 128, 96, 16), (5, 64, 48, 32), (1, 300, 260, 16)])
+@pytest.mark.parametrize("H,row,vd,page", [(6, 144, 112, 16), (3, 56, 40, 8), (2, 128, 96, 16), (5, 64, 48, 32), (1, 300, 260, 16),
+                                           (8, 192, 128, 16), (32, 256, 192, 16), (3, 96, 64, 8), (7, 104, 32, 16), (128, 64, 64, 16)])
 @pytest.mark.parametrize("q_lens,ctx", [((1, 1, 1), (257, 64, 1)), ((70, 5), (70, 133)), ((1, 40, 1, 2), (100, 300, 17, 2))])
 def test_latent_attention_kernels(K, dtype, H, row, vd, page, q_lens, ctx):
     """Decoded tokens alone (key splits), prompt portions behind a prefix, and both in one step; rows of the sizes
-    the tensor-core kernel is built for and of sizes it is not (the plain kernel, rows beyond 256 elements)."""
+    the tensor-core kernels are built for (tcgen05 for portions where the value is a multiple of 32, mma.sync where row and
+    value are multiples of 16) and of sizes they are not (the plain kernel, rows beyond 256 elements)."""
     rows = [rnd(c, row, seed=20 + i).to(dtype).double() for i, c in enumerate(ctx)]
     T = sum(q_lens)
     q, gate = rnd(T, H, row, seed=30, scale=1.5).to(dtype), torch.rand(T, H, generator=torch.Generator().manual_seed(1))
@@ -161,13 +163,16 @@ def test_latent_attention_kernels(K, dtype, H, row, vd, page, q_lens, ctx):
     got = K.latent_attention(q.cuda(), cache, meta, H, row, vd, 0.11, gate=gate.cuda())
     want = plain_latent(q.double(), rows, q_lens, vd, 0.11, gate.double())
     assert got.shape == (T, H, vd) and rel_err(got, want) < (3e-5 if dtype == torch.float32 else 2e-2)
-    if dtype == torch.bfloat16 and row % 16 == 0 and vd % 16 == 0 and row <= 256:      # both kernels are the same function
-        K.LATENT_FLASH = False
+    if dtype == torch.bfloat16 and row <= 256:      # the kernels are the same function
+        K.LATENT_TCGEN05 = False
         try:
+            flash = K.latent_attention(q.cuda(), cache, meta, H, row, vd, 0.11, gate=gate.cuda())
+            K.LATENT_FLASH = False
             slow = K.latent_attention(q.cuda(), cache, meta, H, row, vd, 0.11, gate=gate.cuda())
         finally:
-            K.LATENT_FLASH = True
-        assert rel_err(got, slow) < 2e-2
+            K.LATENT_FLASH = K.LATENT_TCGEN05 = True
+        assert rel_err(got, slow) < 2e-2 and rel_err(flash, slow) < 2e-2
+        K.raise_on_abort()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
