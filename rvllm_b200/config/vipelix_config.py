@@ -143,8 +143,8 @@ class VipelixConfig:
             start = integer(raw_loop, "start", "loop: ", minimum=0)
             stop = integer(raw_loop, "stop", "loop: ", minimum=0)
             times = integer(raw_loop, "times", "loop: ")
-            if not (0 <= start < stop <= len(raw_layers)):
-                p.append(f"loop: start {start} and stop {stop} must name a non-empty span of the {len(raw_layers)} layers")
+            if not (0 <= start <= stop <= len(raw_layers)):
+                p.append(f"loop: start {start} and stop {stop} must name a span of the {len(raw_layers)} layers")
             loop = (start, stop, times)
         cap = obj.get("logit_softcap")
         if cap is not None and (not _is_num(cap) or not cap > 0):
@@ -198,7 +198,7 @@ class VipelixConfig:
     def run_plan(self) -> List[Tuple[int, Optional[int]]]:
         """(layer, pass) in execution order; pass is the number of the pass that the entry opens, else None."""
         n = len(self.layers)
-        if self.loop is None:
+        if self.loop is None or self.loop[0] == self.loop[1]:       # no span, or an empty one: every layer once, nothing between
             return [(i, None) for i in range(n)]
         start, stop, times = self.loop
         plan: List[Tuple[int, Optional[int]]] = [(i, None) for i in range(start)]
@@ -249,4 +249,6 @@ class VipelixConfig:
             lm_head_name=None,
             position_encodings={key: PartSpec("rotary", {"head_dim": rd, "theta": base, "rotary_dim": dims})
                                 for (rd, dims, base), key in rotations.items()},
-            logit_hooks=hooks, residual_dtype="float32", eos_token_ids=self.eos_token_ids)
+            logit_hooks=hooks, residual_dtype="float32", eos_token_ids=self.eos_token_ids,
+            # (an empty span opens no pass: its table of pass vectors, if the checkpoint has one, is never read)
+            ignored_tensors=("loop.step",) if self.loop is not None and self.loop[0] == self.loop[1] else ())

@@ -58,6 +58,11 @@ def test_config_round_trip_and_spec():
     plain = config_from_dict(X.odd_shapes()).to_spec()
     assert [(e.layer, len(e.before)) for e in plain.run_order] == [(0, 0), (1, 0)] and "loop.step" not in expected_tensors(plain)
     assert [h.kind for h in plain.logit_hooks] == ["logit_softcap"] and not config_from_dict(X.small_b()).to_spec().logit_hooks
+    # an empty span is no span: no pass is opened, and a table of pass vectors in the checkpoint is left alone
+    empty = X.small_a()
+    empty["loop"] = {"start": 2, "stop": 2, "times": 5}
+    spec = config_from_dict(empty).to_spec()
+    assert [(e.layer, len(e.before)) for e in spec.run_order] == [(0, 0), (1, 0), (2, 0), (3, 0)] and spec.ignored_tensors == ("loop.step",)
 
 
 def test_config_problems_are_collected():
@@ -67,7 +72,7 @@ def test_config_problems_are_collected():
     bad["layers"][1]["mlp"]["router"]["top"] = 9           # of 5 experts
     bad["layers"][2]["type"] = "attention"
     bad["layers"][3]["mlp"] = {"kind": "wide"}
-    bad["loop"] = {"start": 3, "stop": 2, "times": 0}
+    bad["loop"] = {"start": 3, "stop": 2, "times": 0}          # a span that ends before it starts
     bad["logit_softcap"] = -1
     with pytest.raises(ConfigError) as e:
         config_from_dict(bad)
